@@ -1,0 +1,300 @@
+/*
+ * tenferro_b200.h - C ABI of libtenferro_b200.so
+ *
+ * A B200 (sm_100a) backend for the contraction hot path of tenferro-rs: the
+ * `TensorPrims<A>` describe -> plan -> execute protocol and the N-ary einsum
+ * contraction-tree executor.  Everything here is plain C: pointers, sizes and
+ * integer status codes.  A Rust `CudaBackend: TensorPrims<Standard>` (or any
+ * other FFI user) binds exactly these entry points.
+ *
+ * The reference has no FFI of its own (its C FFI is a stated future goal,
+ * AGENTS.md:19-20), so each entry point cites the Rust item whose semantics
+ * it carries.
+ *
+ * Conventions
+ *  - Every function returns a tfb_status; TFB_OK is 0.  On failure a
+ *    thread-local message is available from tfb_last_error().  Nothing
+ *    aborts or throws across this boundary.
+ *  - Strides and offsets are signed and counted in ELEMENTS of the dtype,
+ *    as in `Tensor<T>` (tenferro-tensor/src/lib.rs:167-171).
+ *  - `base` pointers in views are DEVICE pointers.
+ *  - Work is enqueued on the context's stream and the call returns without
+ *    waiting (tenferro-einsum/src/lib.rs:146-177).  Use events or
+ *    tfb_ctx_synchronize() before touching results from the host.
+ *  - Complex numbers are interleaved (re, im) pairs.
+ */
+#ifndef TENFERRO_B200_H
+#define TENFERRO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ */
+/* Status codes: one per variant of tenferro_device::Error            */
+/* (tenferro-device/src/lib.rs:109-159).                              */
+/* ------------------------------------------------------------------ */
+typedef enum tfb_status {
+    TFB_OK = 0,
+    TFB_ERR_SHAPE_MISMATCH = 1,       /* Error::ShapeMismatch              */
+    TFB_ERR_RANK_MISMATCH = 2,        /* Error::RankMismatch               */
+    TFB_ERR_DEVICE = 3,               /* Error::DeviceError(String)        */
+    TFB_ERR_NO_COMPATIBLE_DEVICE = 4, /* Error::NoCompatibleComputeDevice  */
+    TFB_ERR_CROSS_MEMORY_SPACE = 5,   /* Error::CrossMemorySpaceOperation  */
+    TFB_ERR_INVALID_ARGUMENT = 6,     /* Error::InvalidArgument(String)    */
+    TFB_ERR_STRIDED = 7               /* Error::Strided(StridedError)      */
+} tfb_status;
+
+/* Scalar types with `HasAlgebra<Algebra = Standard>`
+ * (tenferro-algebra/src/lib.rs:58-72).  Names follow num-complex:
+ * C32 = Complex32 = two f32, C64 = Complex64 = two f64. */
+typedef enum tfb_dtype {
+    TFB_F32 = 0,
+    TFB_F64 = 1,
+    TFB_C32 = 2,
+    TFB_C64 = 3
+} tfb_dtype;
+
+/* PrimDescriptor variants (tenferro-prims/src/lib.rs:152-245). */
+typedef enum tfb_op {
+    TFB_OP_BATCHED_GEMM = 0,
+    TFB_OP_REDUCE = 1,
+    TFB_OP_TRACE = 2,
+    TFB_OP_PERMUTE = 3,
+    TFB_OP_ANTI_TRACE = 4,
+    TFB_OP_ANTI_DIAG = 5,
+    TFB_OP_CONTRACT = 6,
+    TFB_OP_ELEMENTWISE_MUL = 7
+} tfb_op;
+
+/* ReduceOp (tenferro-prims/src/lib.rs:100-107). */
+typedef enum tfb_reduce_op { TFB_REDUCE_SUM = 0, TFB_REDUCE_MAX = 1, TFB_REDUCE_MIN = 2 } tfb_reduce_op;
+
+/* Extension (tenferro-prims/src/lib.rs:123-128). */
+typedef enum tfb_extension { TFB_EXT_CONTRACT = 0, TFB_EXT_ELEMENTWISE_MUL = 1 } tfb_extension;
+
+/* OpKind (tenferro-device/src/lib.rs:77-90). */
+typedef enum tfb_op_kind {
+    TFB_KIND_CONTRACT = 0,
+    TFB_KIND_BATCHED_GEMM = 1,
+    TFB_KIND_REDUCE = 2,
+    TFB_KIND_TRACE = 3,
+    TFB_KIND_PERMUTE = 4,
+    TFB_KIND_ELEMENTWISE_MUL = 5
+} tfb_op_kind;
+
+/* LogicalMemorySpace (tenferro-device/src/lib.rs:30-38). */
+typedef enum tfb_space_kind { TFB_SPACE_MAIN_MEMORY = 0, TFB_SPACE_GPU_MEMORY = 1 } tfb_space_kind;
+
+/* ComputeDevice (tenferro-device/src/lib.rs:46-72). */
+typedef enum tfb_device_kind { TFB_DEVICE_CPU = 0, TFB_DEVICE_CUDA = 1, TFB_DEVICE_HIP = 2 } tfb_device_kind;
+typedef struct tfb_compute_device {
+    int32_t kind;      /* tfb_device_kind */
+    int32_t device_id; /* zero-based */
+} tfb_compute_device;
+
+/*
+ * One PrimDescriptor.  Only the fields of the chosen variant are read:
+ *   BATCHED_GEMM   batch_dims[n_batch_dims], m, n, k.  Shapes are
+ *                  A[batch..., m, k], B[batch..., k, n], C[batch..., m, n]
+ *                  (tenferro-prims/src/lib.rs:156-168).
+ *   REDUCE         modes_a, modes_c, reduce_op              (:170-180)
+ *   TRACE          modes_a, modes_c, paired[2*n_pairs]      (:182-192)
+ *   PERMUTE        modes_a (input), modes_b (output)        (:194-202)
+ *   ANTI_TRACE     modes_a, modes_c, paired                 (:204-212)
+ *   ANTI_DIAG      modes_a, modes_c, paired                 (:214-222)
+ *   CONTRACT       modes_a, modes_b, modes_c                (:227-239)
+ *   ELEMENTWISE_MUL  nothing                                (:241-244)
+ */
+typedef struct tfb_desc {
+    int32_t op; /* tfb_op */
+    int32_t reduce_op; /* tfb_reduce_op */
+    const uint32_t* modes_a;
+    size_t n_modes_a;
+    const uint32_t* modes_b;
+    size_t n_modes_b;
+    const uint32_t* modes_c;
+    size_t n_modes_c;
+    const uint32_t* paired; /* (first, second) label pairs, flattened */
+    size_t n_pairs;
+    const size_t* batch_dims;
+    size_t n_batch_dims;
+    size_t m, n, k;
+} tfb_desc;
+
+/* View flags. */
+#define TFB_VIEW_CONJ 1u /* operand is read as its complex conjugate (lazy Tensor::conj,
+                            tenferro-tensor/src/lib.rs:606-658); ignored for real dtypes;
+                            not allowed on outputs */
+
+/* A strided device view: the fields of `Tensor<T>` / `StridedView<T>`
+ * (tenferro-tensor/src/lib.rs:167-171, 198-211). */
+typedef struct tfb_view {
+    void* base;               /* device pointer to element 0 of the buffer */
+    size_t rank;
+    const size_t* dims;       /* [rank] */
+    const ptrdiff_t* strides; /* [rank], in elements, may be 0 or negative */
+    ptrdiff_t offset;         /* in elements, added to base */
+    uint32_t flags;           /* TFB_VIEW_* */
+} tfb_view;
+
+typedef struct tfb_ctx tfb_ctx;     /* one per CUDA device in use */
+typedef struct tfb_plan tfb_plan;   /* TensorPrims::Plan<T>, immutable after creation */
+typedef struct tfb_event tfb_event; /* CompletionEvent */
+typedef struct tfb_subscripts tfb_subscripts; /* tenferro_einsum::Subscripts */
+typedef struct tfb_tree tfb_tree;   /* tenferro_einsum::ContractionTree */
+
+/* ------------------------------------------------------------------ */
+/* Errors                                                              */
+/* ------------------------------------------------------------------ */
+/* Copy the calling thread's last error message (NUL-terminated) into buf.
+ * Returns the full message length. */
+size_t tfb_last_error(char* buf, size_t cap);
+/* Library version string. */
+const char* tfb_version(void);
+
+/* ------------------------------------------------------------------ */
+/* tenferro-device: context, stream, stream-ordered pool, events       */
+/* ------------------------------------------------------------------ */
+/* Create the context of CUDA device `device_id` = ComputeDevice::Cuda{device_id}
+ * computing on LogicalMemorySpace::GpuMemory{space_id: device_id}.
+ * Fails with TFB_ERR_DEVICE when no usable GPU is present (there is no CPU path). */
+tfb_status tfb_ctx_create(int device_id, tfb_ctx** out);
+tfb_status tfb_ctx_destroy(tfb_ctx* ctx);
+tfb_status tfb_ctx_device(const tfb_ctx* ctx, int* device_id);
+/* The CUDA stream (cudaStream_t) all work of this context is enqueued on. */
+tfb_status tfb_ctx_stream(const tfb_ctx* ctx, void** stream);
+/* Enqueue on a caller-owned stream instead (NULL restores the context's own). */
+tfb_status tfb_ctx_set_stream(tfb_ctx* ctx, void* stream);
+tfb_status tfb_ctx_synchronize(tfb_ctx* ctx);
+/* Number of SMs and bytes of device memory, as reported by the driver. */
+tfb_status tfb_ctx_properties(const tfb_ctx* ctx, int* sm_count, size_t* total_mem, int* cc_major, int* cc_minor);
+
+/* Stream-ordered allocation from the device's memory pool: the block is usable by
+ * work enqueued after this call and is returned to the pool after work enqueued
+ * before tfb_free has finished. */
+tfb_status tfb_alloc(tfb_ctx* ctx, size_t bytes, void** out);
+tfb_status tfb_free(tfb_ctx* ctx, void* ptr);
+/* Bytes currently reserved / in use by the pool. */
+tfb_status tfb_pool_stats(tfb_ctx* ctx, size_t* reserved, size_t* used);
+
+tfb_status tfb_memcpy_h2d_async(tfb_ctx* ctx, void* dst, const void* src, size_t bytes);
+tfb_status tfb_memcpy_d2h_async(tfb_ctx* ctx, void* dst, const void* src, size_t bytes);
+tfb_status tfb_memcpy_d2d_async(tfb_ctx* ctx, void* dst, const void* src, size_t bytes);
+/* GpuMemory{src_device} -> GpuMemory{dst_device} over NVLink
+ * (Tensor::to_memory_space_async, tenferro-tensor/src/lib.rs:660-671). */
+tfb_status tfb_memcpy_p2p_async(tfb_ctx* ctx, void* dst, int dst_device, const void* src, int src_device, size_t bytes);
+tfb_status tfb_memset_async(tfb_ctx* ctx, void* dst, int value, size_t bytes);
+/* Page-locked host memory for asynchronous transfers. */
+tfb_status tfb_host_alloc(size_t bytes, void** out);
+tfb_status tfb_host_free(void* ptr);
+
+/* CompletionEvent (tenferro-tensor/src/lib.rs:301-309, 677-713). */
+tfb_status tfb_event_record(tfb_ctx* ctx, tfb_event** out);    /* marks all work enqueued so far */
+tfb_status tfb_event_wait(tfb_ctx* ctx, tfb_event* ev);        /* later work of ctx waits for ev; host does not block */
+tfb_status tfb_event_synchronize(tfb_event* ev);               /* Tensor::wait */
+tfb_status tfb_event_query(tfb_event* ev, int* ready);         /* Tensor::is_ready */
+tfb_status tfb_event_elapsed_ms(tfb_event* start, tfb_event* stop, float* ms);
+tfb_status tfb_event_destroy(tfb_event* ev);
+
+/* preferred_compute_devices (tenferro-device/src/lib.rs:92-105): devices able to run
+ * `op_kind` on the given memory space, most preferred first.  MainMemory has none here
+ * (-> TFB_ERR_NO_COMPATIBLE_DEVICE): this library has no CPU path. */
+tfb_status tfb_preferred_compute_devices(int32_t space_kind, size_t space_id, int32_t op_kind,
+                                         tfb_compute_device* out, size_t cap, size_t* n_out);
+/* Display of ComputeDevice: "cpu:0", "cuda:1", "hip:2" (tenferro-device/src/lib.rs:62-72). */
+size_t tfb_compute_device_format(tfb_compute_device dev, char* buf, size_t cap);
+
+/* ------------------------------------------------------------------ */
+/* tenferro-prims: TensorPrims<Standard> for the CUDA backend          */
+/* ------------------------------------------------------------------ */
+/* TensorPrims::has_extension_for::<T>(ext) (tenferro-prims/src/lib.rs:322-339). */
+int tfb_has_extension(int32_t dtype, int32_t ext);
+
+/* TensorPrims::plan::<T>(desc, shapes) (tenferro-prims/src/lib.rs:282-298).
+ * shapes: inputs first, then the output.  Validates the descriptor against the shapes,
+ * classifies modes and selects the kernel family.  ctx may be NULL to validate only;
+ * such a plan cannot be executed. */
+tfb_status tfb_plan_create(tfb_ctx* ctx, const tfb_desc* desc, int32_t dtype, size_t n_shapes,
+                           const size_t* ranks, const size_t* const* dims, tfb_plan** out);
+tfb_status tfb_plan_destroy(tfb_plan* plan);
+/* Name of the kernel family the most recent tfb_execute of this plan used (for logs). */
+const char* tfb_plan_kernel_name(const tfb_plan* plan);
+/* Pin the contraction kernel family of a plan: 0 automatic (the default), 1 SIMT,
+ * 2 FP64 tensor pipe (f64/c64), 3 tcgen05 3xTF32 (f32/c32).  "Pre-computes kernel
+ * selection" (tenferro-prims/src/lib.rs:284-286) made visible so the families can be
+ * checked against each other; a forced family that cannot run the layout is an error. */
+tfb_status tfb_plan_force_kernel(tfb_plan* plan, int kernel);
+
+/* TensorPrims::execute (tenferro-prims/src/lib.rs:300-320):
+ *   output = alpha * op(inputs) + beta * output
+ * alpha and beta point to one host scalar of the plan's dtype.  beta == 0 overwrites
+ * the output without reading it.  Views must match the plan's shapes. */
+tfb_status tfb_execute(tfb_plan* plan, const void* alpha, size_t n_inputs, const tfb_view* inputs,
+                       const void* beta, const tfb_view* output);
+
+/* Grouped (ragged) matrix products in one persistent launch:
+ *   C_p[m_p, n_p] = alpha * A_p[m_p, k_p] * B_p[k_p, n_p] + beta * C_p   for p in 0..n_problems.
+ * `PrimDescriptor::BatchedGemm` covers uniform batches only
+ * (tenferro-prims/src/lib.rs:156-168); this entry point carries the same formula to a
+ * table of problems with individual sizes.  Strides are in elements. */
+typedef struct tfb_gemm_problem {
+    int64_t m, n, k;
+    const void* a; int64_t a_rs, a_cs; /* A[i,l] at a + i*a_rs + l*a_cs */
+    const void* b; int64_t b_rs, b_cs; /* B[l,j] at b + l*b_rs + j*b_cs */
+    void* c;       int64_t c_rs, c_cs; /* C[i,j] at c + i*c_rs + j*c_cs */
+} tfb_gemm_problem;
+/* `problems` is a HOST array; it is copied to the device by this call. */
+tfb_status tfb_grouped_gemm(tfb_ctx* ctx, int32_t dtype, size_t n_problems, const tfb_gemm_problem* problems,
+                            const void* alpha, const void* beta);
+
+/* ------------------------------------------------------------------ */
+/* tenferro-einsum: Subscripts, ContractionTree, executor              */
+/* ------------------------------------------------------------------ */
+/* Subscripts::new (tenferro-einsum/src/lib.rs:253-258). */
+tfb_status tfb_subscripts_new(size_t n_inputs, const size_t* input_ranks, const uint32_t* const* inputs,
+                              size_t output_rank, const uint32_t* output, tfb_subscripts** out);
+/* Subscripts::parse (tenferro-einsum/src/lib.rs:260-283): "ij,jk->ik"; letters a-z, A-Z;
+ * parentheses fix the pairwise order, e.g. "ij,(jk,kl)->il". */
+tfb_status tfb_subscripts_parse(const char* notation, tfb_subscripts** out);
+tfb_status tfb_subscripts_destroy(tfb_subscripts* subs);
+size_t tfb_subscripts_n_inputs(const tfb_subscripts* subs);
+size_t tfb_subscripts_input(const tfb_subscripts* subs, size_t i, uint32_t* labels, size_t cap);
+size_t tfb_subscripts_output(const tfb_subscripts* subs, uint32_t* labels, size_t cap);
+/* 1 when the notation carried parentheses.  The grouping is kept inside the subscripts and
+ * honoured by tfb_tree_optimize: each parenthesised group is contracted to one
+ * intermediate before it meets its siblings. */
+int tfb_subscripts_has_order(const tfb_subscripts* subs);
+
+/* ContractionTree::optimize (tenferro-einsum/src/lib.rs:303-318): minimises the total
+ * multiply-add count (exact search for up to 12 operands per group, greedy beyond). */
+tfb_status tfb_tree_optimize(const tfb_subscripts* subs, const size_t* ranks, const size_t* const* dims,
+                             tfb_tree** out);
+/* ContractionTree::from_pairs (tenferro-einsum/src/lib.rs:320-355): intermediates are
+ * numbered from n_inputs upward in the order they are produced. */
+tfb_status tfb_tree_from_pairs(const tfb_subscripts* subs, const size_t* ranks, const size_t* const* dims,
+                               size_t n_pairs, const size_t* pairs, tfb_tree** out);
+tfb_status tfb_tree_destroy(tfb_tree* tree);
+size_t tfb_tree_n_steps(const tfb_tree* tree);
+size_t tfb_tree_pairs(const tfb_tree* tree, size_t* pairs, size_t cap);
+/* Multiply-adds of the whole tree (real or complex, whichever the operands are). */
+double tfb_tree_macs(const tfb_tree* tree);
+size_t tfb_tree_output_dims(const tfb_tree* tree, size_t* dims, size_t cap);
+
+/* einsum_with_plan_into (tenferro-einsum/src/lib.rs:584-621):
+ *   output = alpha * einsum(operands) + beta * output
+ * walking the tree with every intermediate kept in the context's pool.  The allocating
+ * variants (einsum_with_plan, :415-430) are this call on a fresh column-major output
+ * with alpha = 1, beta = 0; the `_owned` variants (:482-498) additionally let the
+ * caller release operands right after the call returns. */
+tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t dtype, size_t n_operands,
+                                     const tfb_view* operands, const void* alpha, const void* beta,
+                                     const tfb_view* output);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENFERRO_B200_H */

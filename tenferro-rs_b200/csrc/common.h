@@ -1,0 +1,178 @@
+// Internal declarations shared by the host side and the kernels of libtenferro_b200.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/tenferro_b200.h"
+
+namespace tfb {
+
+// ---------------------------------------------------------------- errors
+// Sets the calling thread's message and returns `code`, so call sites read
+// `return fail(TFB_ERR_..., "...")`.
+tfb_status fail(tfb_status code, const char* fmt, ...);
+void set_error(const char* msg);
+
+#define TFB_CUDA(expr)                                                                         \
+    do {                                                                                       \
+        cudaError_t e__ = (expr);                                                              \
+        if (e__ != cudaSuccess)                                                                \
+            return ::tfb::fail(TFB_ERR_DEVICE, "%s failed: %s (%s:%d)", #expr,                 \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);                   \
+    } while (0)
+
+#define TFB_TRY(expr)                    \
+    do {                                 \
+        tfb_status s__ = (expr);         \
+        if (s__ != TFB_OK) return s__;   \
+    } while (0)
+
+inline size_t dtype_size(int dt) {
+    switch (dt) {
+        case TFB_F32: return 4;
+        case TFB_F64: return 8;
+        case TFB_C32: return 8;
+        case TFB_C64: return 16;
+    }
+    return 0;
+}
+inline bool dtype_is_complex(int dt) { return dt == TFB_C32 || dt == TFB_C64; }
+inline bool dtype_valid(int dt) { return dt >= 0 && dt <= 3; }
+
+// A host scalar of any dtype, widened to complex double.
+struct Scalar {
+    double re = 0, im = 0;
+    bool is_zero() const { return re == 0 && im == 0; }
+    bool is_one() const { return re == 1 && im == 0; }
+};
+Scalar load_scalar(int dtype, const void* p);
+
+}  // namespace tfb
+
+// ---------------------------------------------------------------- context
+struct tfb_ctx {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;  // own_stream or a caller-provided one
+    cudaMemPool_t pool = nullptr;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    size_t total_mem = 0;
+    size_t smem_optin = 0;
+    // One-word device status used by kernels with bounded waits (0 = fine).
+    int* dev_status = nullptr;
+};
+
+struct tfb_event {
+    cudaEvent_t ev = nullptr;
+    int device = 0;
+};
+
+namespace tfb {
+
+// Scoped `cudaSetDevice` that restores the caller's device.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// ------------------------------------------------------------ strided ops
+constexpr int kMaxRank = 12;  // after fusing adjacent modes
+
+// A loop nest over up to kMaxRank fused modes and up to three tensors.
+// Passed to kernels by value.
+struct LoopNest {
+    int rank = 0;
+    int64_t extent[kMaxRank];
+    int64_t stride[3][kMaxRank];  // element strides of tensors 0..2 (0 where absent)
+    int64_t total = 1;            // product of extents
+};
+
+// One mode of a normalised operation: extent and per-tensor element stride.
+struct Mode {
+    int64_t extent;
+    int64_t s[3];
+};
+
+// Sort `modes` by |stride| of tensor `key` ascending and fuse neighbours that are
+// contiguous in every tensor.  Extent-1 modes vanish.
+void sort_and_fuse(std::vector<Mode>& modes, int key, int n_tensors);
+// Fuse neighbours only (keeps order).
+void fuse_in_order(std::vector<Mode>& modes, int n_tensors);
+tfb_status make_nest(const std::vector<Mode>& modes, LoopNest* out);
+
+// Validated view: element pointer already offset, dims/strides as int64.
+struct HView {
+    char* ptr = nullptr;  // base + offset * sizeof(T)
+    std::vector<int64_t> dims, strides;
+    bool conj = false;
+};
+tfb_status to_hview(const tfb_view& v, int dtype, HView* out, const char* what);
+
+// ------------------------------------------------------------ kernel entry points (host launchers)
+// out[idx_out] = alpha * (conj?)in[idx_in] + beta * out[idx_out] over nest (tensor 0 = in, 1 = out).
+tfb_status launch_permute(tfb_ctx* ctx, int dtype, const LoopNest& nest, const void* in, void* out, Scalar alpha,
+                          Scalar beta, bool conj);
+// out = alpha * a * b + beta * out (tensors 0,1 = a,b; 2 = out).
+tfb_status launch_elementwise_mul(tfb_ctx* ctx, int dtype, const LoopNest& nest, const void* a, const void* b,
+                                  void* out, Scalar alpha, Scalar beta, bool conj_a, bool conj_b);
+// out[kept] = alpha * reduce_op over `red` of in + beta * out.  kept: tensors (0 = in, 1 = out), red: tensor 0.
+tfb_status launch_reduce(tfb_ctx* ctx, int dtype, int op, const LoopNest& kept, const LoopNest& red, const void* in,
+                         void* out, Scalar alpha, Scalar beta, bool conj);
+// out = beta * out over nest (tensor 0 = out).  beta == 0 writes zeros.
+tfb_status launch_scale(tfb_ctx* ctx, int dtype, const LoopNest& nest, void* out, Scalar beta);
+
+// Normalised contraction: C[b,m,n] = alpha * sum_k A[b,m,k] B[b,k,n] + beta * C.
+// Each group is a list of fused modes; tensor index 0 = A, 1 = B, 2 = C.
+struct ContractProblem {
+    int dtype = TFB_F64;
+    std::vector<Mode> batch, m, n, k;
+    const void* a = nullptr;
+    const void* b = nullptr;
+    void* c = nullptr;
+    bool conj_a = false, conj_b = false;
+    Scalar alpha, beta;
+    int64_t M() const;
+    int64_t N() const;
+    int64_t K() const;
+    int64_t B() const;
+};
+enum ContractKernel { CK_AUTO = 0, CK_SIMT = 1, CK_DMMA = 2, CK_TCGEN05 = 3 };
+// Runs the problem on ctx's stream.  `used` receives the kernel family chosen.
+tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_kernel, const char** used);
+
+// Family-specific launchers (each may decline with *declined = true and TFB_OK).
+tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p);
+tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
+tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
+
+tfb_status grouped_gemm_launch(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, Scalar alpha,
+                               Scalar beta);
+
+// Scratch from the context pool, released stream-ordered when the object dies.
+struct PoolBlock {
+    tfb_ctx* ctx = nullptr;
+    void* ptr = nullptr;
+    ~PoolBlock();
+    tfb_status alloc(tfb_ctx* c, size_t bytes);
+};
+
+int env_int(const char* name, int dflt);
+
+}  // namespace tfb

@@ -1,0 +1,61 @@
+// Shared device-side pieces of the contraction kernels: the argument block, the offset
+// ("scatter") tables that carry arbitrary strides into the GEMM main loop, and the
+// cp.async helpers.
+//
+// A contraction `C[modes_c] = alpha * A[modes_a] . B[modes_b] + beta * C`
+// (tenferro-prims/src/lib.rs:227-239) is normalised on the host into four mode groups:
+// batch (in A, B and C), M (A and C), N (B and C), K (A and B).  Each group is linearised,
+// and for every linear index the element offset it contributes in each tensor is tabulated
+// once:   addr(A[b,m,k]) = a + a_b[b] + a_m[m] + a_k[k]   and likewise for B and C.
+// That is the whole "permute" of permute-into-GEMM: tiles are gathered straight from the
+// strided operands, nothing is packed in global memory.
+#pragma once
+#include "common.h"
+
+namespace tfb {
+
+struct ContractArgs {
+    const char* a;
+    const char* b;
+    char* c;
+    const int64_t* a_b;
+    const int64_t* b_b;
+    const int64_t* c_b;
+    const int64_t* a_m;
+    const int64_t* c_m;
+    const int64_t* b_n;
+    const int64_t* c_n;
+    const int64_t* a_k;
+    const int64_t* b_k;
+    int64_t M, N, K, B;
+    double alpha_re, alpha_im, beta_re, beta_im;
+    int conj_a, conj_b;
+    int a_kfast, b_kfast;  // 1: the unit-stride direction of the operand tile is K; 0: M (resp. N)
+    int a_vec, b_vec;      // elements per cp.async (1, or 2 for f64 when 16-byte chunks are legal)
+    // Work decomposition: tiles x k-iterations, cut into equal contiguous ranges ("stream-K").
+    int64_t tiles_m, tiles_n, n_tiles, k_iters, total_iters, iters_per_cta;
+    char* partial;  // 2 slots of one block tile per CTA, used only by ranges that cut a tile
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_8(void* smem, const void* gmem, bool valid) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    int sz = valid ? 8 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_4(void* smem, const void* gmem, bool valid) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    int sz = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(s), "l"(gmem), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+}  // namespace tfb
