@@ -192,6 +192,19 @@ tfb_status tfb_memset_async(tfb_ctx* ctx, void* dst, int value, size_t bytes);
 tfb_status tfb_host_alloc(size_t bytes, void** out);
 tfb_status tfb_host_free(void* ptr);
 
+/* Measurement support (no counterpart in the reference, which has no benchmarks).
+ * tfb_kernel_launch_count: kernels this library has launched in this process.
+ * tfb_ctx_profile_begin/read/end: while on, every launch is bracketed by a CUDA event pair on
+ * the launching stream; read() waits for the stream and returns the number of launches and
+ * the summed device time of the kernel family `kernel` ("contract_dmma", "permute_tiled", ...).
+ * tfb_probe_*: peak probes - DMMA on register operands (TFLOP/s), streaming copy (GB/s). */
+unsigned long long tfb_kernel_launch_count(void);
+tfb_status tfb_ctx_profile_begin(tfb_ctx* ctx);
+tfb_status tfb_ctx_profile_read(tfb_ctx* ctx, const char* kernel, size_t* launches, double* total_ms);
+tfb_status tfb_ctx_profile_end(tfb_ctx* ctx);
+tfb_status tfb_probe_fp64_tflops(tfb_ctx* ctx, double* tflops);
+tfb_status tfb_probe_hbm_gbs(tfb_ctx* ctx, double* gbs);
+
 /* CompletionEvent (tenferro-tensor/src/lib.rs:301-309, 677-713). */
 tfb_status tfb_event_record(tfb_ctx* ctx, tfb_event** out);    /* marks all work enqueued so far */
 tfb_status tfb_event_wait(tfb_ctx* ctx, tfb_event* ev);        /* later work of ctx waits for ev; host does not block */

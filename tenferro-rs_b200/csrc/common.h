@@ -70,6 +70,13 @@ struct tfb_ctx {
     size_t smem_optin = 0;
     // One-word device status used by kernels with bounded waits (0 = fine).
     int* dev_status = nullptr;
+    // Optional per-launch timing (tfb_ctx_profile_*): event pairs around named launches.
+    bool profiling = false;
+    struct ProfRec {
+        const char* name;
+        cudaEvent_t start, stop;
+    };
+    std::vector<ProfRec> prof;
 };
 
 struct tfb_event {
@@ -174,5 +181,15 @@ struct PoolBlock {
 };
 
 int env_int(const char* name, int dflt);
+
+// Counts kernel launches of this library (process-wide) and, while profiling is on, brackets
+// the launch with an event pair on the launching stream.
+void count_launch(int n = 1);
+struct LaunchScope {
+    tfb_ctx* ctx;
+    cudaEvent_t stop = nullptr;
+    LaunchScope(tfb_ctx* c, const char* name);
+    ~LaunchScope();
+};
 
 }  // namespace tfb

@@ -5,9 +5,11 @@
 // 660-713 (CompletionEvent, to_memory_space_async, wait, is_ready).
 #include "common.h"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace tfb {
+unsigned long long launch_count();
 
 static thread_local std::string g_last_error;
 
@@ -43,6 +45,27 @@ Scalar load_scalar(int dtype, const void* p) {
         case TFB_C64: s.re = ((const double*)p)[0]; s.im = ((const double*)p)[1]; break;
     }
     return s;
+}
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch(int n) { g_launches += (unsigned long long)n; }
+unsigned long long launch_count() { return g_launches.load(); }
+
+LaunchScope::LaunchScope(tfb_ctx* c, const char* name) : ctx(c) {
+    count_launch(1);
+    if (!c->profiling) return;
+    cudaEvent_t start;
+    if (cudaEventCreate(&start) != cudaSuccess) return;
+    if (cudaEventCreate(&stop) != cudaSuccess) {
+        cudaEventDestroy(start);
+        stop = nullptr;
+        return;
+    }
+    cudaEventRecord(start, c->stream);
+    c->prof.push_back({name, start, stop});
+}
+LaunchScope::~LaunchScope() {
+    if (stop) cudaEventRecord(stop, ctx->stream);
 }
 
 PoolBlock::~PoolBlock() {
@@ -113,6 +136,47 @@ tfb_status tfb_ctx_create(int device_id, tfb_ctx** out) {
     TFB_CUDA(cudaMalloc(&c->dev_status, sizeof(int)));
     TFB_CUDA(cudaMemset(c->dev_status, 0, sizeof(int)));
     *out = c.release();
+    return TFB_OK;
+}
+
+unsigned long long tfb_kernel_launch_count(void) { return launch_count(); }
+
+tfb_status tfb_ctx_profile_begin(tfb_ctx* ctx) {
+    if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_profile_begin: ctx is NULL");
+    for (auto& r : ctx->prof) {
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    ctx->prof.clear();
+    ctx->profiling = true;
+    return TFB_OK;
+}
+
+tfb_status tfb_ctx_profile_read(tfb_ctx* ctx, const char* kernel, size_t* launches, double* total_ms) {
+    if (!ctx || !kernel || !launches || !total_ms)
+        return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_profile_read: NULL argument");
+    DeviceGuard g(ctx->device);
+    TFB_CUDA(cudaStreamSynchronize(ctx->stream));
+    *launches = 0;
+    *total_ms = 0;
+    for (auto& r : ctx->prof) {
+        if (strcmp(r.name, kernel) != 0) continue;
+        float ms = 0;
+        TFB_CUDA(cudaEventElapsedTime(&ms, r.start, r.stop));
+        *total_ms += ms;
+        ++*launches;
+    }
+    return TFB_OK;
+}
+
+tfb_status tfb_ctx_profile_end(tfb_ctx* ctx) {
+    if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_profile_end: ctx is NULL");
+    ctx->profiling = false;
+    for (auto& r : ctx->prof) {
+        cudaEventDestroy(r.start);
+        cudaEventDestroy(r.stop);
+    }
+    ctx->prof.clear();
     return TFB_OK;
 }
 

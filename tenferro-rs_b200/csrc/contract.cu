@@ -112,6 +112,7 @@ tfb_status get_tables(tfb_ctx* ctx, const ContractProblem& p, std::shared_ptr<Co
     int64_t biggest = std::max(std::max(t->B, t->M), std::max(t->N, t->K));
     int gx = (int)std::min<int64_t>((biggest + 255) / 256, 1024);
     if (gx < 1) gx = 1;
+    LaunchScope ls(ctx, "build_tables");
     build_tables_kernel<<<dim3(gx, 4), 256, 0, ctx->stream>>>(jobs);
     TFB_CUDA(cudaGetLastError());
     // Bounded cache: drop the oldest entry once 256 layouts are held.  Tables in use by
@@ -261,6 +262,7 @@ tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p) {
     a.n_tiles = a.tiles_m * a.tiles_n * a.B;
     if (a.n_tiles == 0) return TFB_OK;
     int grid = (int)std::min<int64_t>(a.n_tiles, (int64_t)ctx->sm_count * 8);
+    LaunchScope ls(ctx, "contract_simt");
     switch (p.dtype) {
         case TFB_F32: contract_simt_kernel<float><<<grid, 256, 0, ctx->stream>>>(a); break;
         case TFB_F64: contract_simt_kernel<double><<<grid, 256, 0, ctx->stream>>>(a); break;

@@ -34,6 +34,7 @@ struct ContractArgs {
     int a_vec, b_vec;      // elements per cp.async (1, or 2 for f64 when 16-byte chunks are legal)
     // Work decomposition: tiles x k-iterations, cut into equal contiguous ranges ("stream-K").
     int64_t tiles_m, tiles_n, n_tiles, k_iters, total_iters, iters_per_cta;
+    int debug;
     char* partial;  // 2 slots of one block tile per CTA, used only by ranges that cut a tile
 };
 

@@ -1,6 +1,7 @@
-// f64 / Complex64 contraction on the FP64 tensor pipe (mma.sync m8n8k4 DMMA).
+// f64 / Complex64 contraction on the FP64 tensor pipe (mma.sync DMMA).
 //
-// tcgen05 has no f64 kind, so double precision runs on the warp-level DMMA instruction.
+// tcgen05 has no f64 kind, so double precision runs on the warp-level DMMA instruction
+// (the m16n8k8 shape: it keeps the pipe fed with a quarter of the instructions of m8n8k4).
 // Operand tiles are gathered from the strided tensors with cp.async through the offset
 // tables (any strides; 16-byte chunks where the layout allows), kept in a multi-stage
 // shared-memory ring, and consumed as m8n8k4 fragments.  Complex64 is four real DMMAs per
@@ -43,25 +44,35 @@ struct DmmaCfg {
 
 __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b) {
     asm("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
-                 : "+d"(c0), "+d"(c1)
-                 : "d"(a), "d"(b));
+        : "+d"(c0), "+d"(c1)
+        : "d"(a), "d"(b));
 }
 
-// Issue the cp.async gathers of one operand tile for k-iteration `kit`.
-//   ROWS x BK elements; `fast_k` says whether threads (and chunks) run along k or along the row index.
-//   row_tab / k_tab: offset tables; r0: first row of the tile; n_rows / K: bounds.
+// m16n8k8: rows gid / gid + 8 of the 16-row tile, k = tig and tig + 4.
+__device__ __forceinline__ void dmma16(double& c0, double& c1, double& c2, double& c3, double a0, double a1, double a2,
+                                       double a3, double b0, double b1) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+d"(c0), "+d"(c1), "+d"(c2), "+d"(c3)
+        : "d"(a0), "d"(a1), "d"(a2), "d"(a3), "d"(b0), "d"(b1));
+}
+
+// Offsets may be negative (reversed axes), so "outside the tensor" is a sentinel no real
+// offset can take, not a sign.
+constexpr int64_t kOutside = INT64_MIN;
+
+// Per-thread state of the cp.async gather of one operand tile (ROWS x BK elements, VEC
+// elements per chunk).  Row offsets are read from the table once per tile; the k offsets of
+// the next k-iteration are fetched one iteration ahead, so no table load sits between a
+// barrier and the copies that follow it.
 template <typename Cfg, int ROWS, int PROW, int VEC>
-__device__ __forceinline__ void gather_tile(char* smem, const char* base, const int64_t* __restrict__ row_tab,
-                                            const int64_t* __restrict__ k_tab, int64_t r0, int64_t n_rows, int64_t k0,
-                                            int64_t K, bool fast_k, int tid) {
-    constexpr int ES = Cfg::ES;
-    constexpr int CHUNKS = ROWS * Cfg::BK / VEC;
-    constexpr int PER_THREAD = (CHUNKS + Cfg::NT - 1) / Cfg::NT;
-#pragma unroll
-    for (int i = 0; i < PER_THREAD; ++i) {
-        int c = tid + i * Cfg::NT;
-        if (CHUNKS % Cfg::NT != 0 && c >= CHUNKS) break;
-        int r, k;
+struct Gather {
+    static constexpr int ES = Cfg::ES;
+    static constexpr int CHUNKS = ROWS * Cfg::BK / VEC;
+    static constexpr int PT = (CHUNKS + Cfg::NT - 1) / Cfg::NT;
+    int64_t row_off[PT];  // element offset of the chunk's row, or kOutside
+    int64_t k_off[PT];    // element offset of the chunk's k for the prefetched iteration, or kOutside
+
+    __device__ __forceinline__ static void coords(int c, bool fast_k, int& r, int& k) {
         if (fast_k) {
             constexpr int KC = Cfg::BK / VEC;
             k = (c % KC) * VEC;
@@ -71,36 +82,64 @@ __device__ __forceinline__ void gather_tile(char* smem, const char* base, const 
             r = (c % RC) * VEC;
             k = c / RC;
         }
-        const bool valid = (r0 + r < n_rows) && (k0 + k < K);
-        const char* src = base;
-        if (valid) src = base + (row_tab[r0 + r] + k_tab[k0 + k]) * (int64_t)ES;
-        char* dst = smem + (size_t)(fast_k ? (r * Cfg::PK + k) : (k * PROW + r)) * ES;
-        if (ES * VEC == 16)
-            cp_async_16(dst, src, valid);
-        else
-            cp_async_8(dst, src, valid);
     }
-}
+    __device__ __forceinline__ void set_tile(const int64_t* __restrict__ row_tab, int64_t r0, int64_t n_rows,
+                                             bool fast_k, int tid) {
+#pragma unroll
+        for (int i = 0; i < PT; ++i) {
+            const int c = tid + i * Cfg::NT;
+            int r, k;
+            coords(c, fast_k, r, k);
+            row_off[i] = (c < CHUNKS && r0 + r < n_rows) ? __ldg(row_tab + r0 + r) : kOutside;
+        }
+    }
+    __device__ __forceinline__ void prefetch(const int64_t* __restrict__ k_tab, int64_t k0, int64_t K, bool fast_k,
+                                             int tid) {
+#pragma unroll
+        for (int i = 0; i < PT; ++i) {
+            const int c = tid + i * Cfg::NT;
+            int r, k;
+            coords(c, fast_k, r, k);
+            k_off[i] = (k0 + k < K) ? __ldg(k_tab + k0 + k) : kOutside;
+        }
+    }
+    __device__ __forceinline__ void issue(char* smem, const char* base, bool fast_k, int tid) const {
+#pragma unroll
+        for (int i = 0; i < PT; ++i) {
+            const int c = tid + i * Cfg::NT;
+            if (CHUNKS % Cfg::NT != 0 && c >= CHUNKS) break;
+            int r, k;
+            coords(c, fast_k, r, k);
+            const bool valid = row_off[i] != kOutside && k_off[i] != kOutside;
+            const char* src = valid ? base + (row_off[i] + k_off[i]) * (int64_t)ES : base;
+            char* dst = smem + (size_t)(fast_k ? (r * Cfg::PK + k) : (k * PROW + r)) * ES;
+            if (ES * VEC == 16)
+                cp_async_16(dst, src, valid);
+            else
+                cp_async_8(dst, src, valid);
+        }
+    }
+};
 
-template <typename Cfg>
-__global__ void __launch_bounds__(Cfg::NT) contract_dmma_kernel(ContractArgs g) {
+template <typename Cfg, int VA, int VB>
+__device__ __forceinline__ void dmma_range(const ContractArgs& g, char* smem, int64_t it_begin, int64_t it_end) {
     constexpr bool CPLX = Cfg::kCplx;
     constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, TM = Cfg::TM, TN = Cfg::TN, STAGES = Cfg::STAGES;
     constexpr int ES = Cfg::ES;
-    extern __shared__ __align__(16) char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm0 = (warp % Cfg::WARPS_M) * Cfg::WM, wn0 = (warp / Cfg::WARPS_M) * Cfg::WN;
     const int lr = lane >> 2, lc = lane & 3;  // fragment row / k (or column pair)
+    const bool a_kfast = g.a_kfast, b_kfast = g.b_kfast;
 
     // Runtime element strides inside the shared tiles.
-    const int a_sm = g.a_kfast ? Cfg::PK : 1, a_sk = g.a_kfast ? 1 : Cfg::PM;
-    const int b_sn = g.b_kfast ? Cfg::PK : 1, b_sk = g.b_kfast ? 1 : Cfg::PN;
+    const int a_sm = a_kfast ? Cfg::PK : 1, a_sk = a_kfast ? 1 : Cfg::PM;
+    const int b_sn = b_kfast ? Cfg::PK : 1, b_sk = b_kfast ? 1 : Cfg::PN;
     const int a_frag = (wm0 + lr) * a_sm + lc * a_sk;
     const int b_frag = (wn0 + lr) * b_sn + lc * b_sk;
-
-    const int64_t it_begin = (int64_t)blockIdx.x * g.iters_per_cta;
-    const int64_t it_end = min(g.total_iters, it_begin + g.iters_per_cta);
     const int64_t first_tile = it_begin / g.k_iters;
+
+    Gather<Cfg, BM, Cfg::PM, VA> ga;
+    Gather<Cfg, BN, Cfg::PN, VB> gb;
 
     int64_t it = it_begin;
     while (it < it_end) {
@@ -114,6 +153,8 @@ __global__ void __launch_bounds__(Cfg::NT) contract_dmma_kernel(ContractArgs g) 
         const int64_t m0 = tm * BM, n0 = tn * BN;
         const char* Ab = g.a + g.a_b[bb] * (int64_t)ES;
         const char* Bb = g.b + g.b_b[bb] * (int64_t)ES;
+        ga.set_tile(g.a_m, m0, g.M, a_kfast, tid);
+        gb.set_tile(g.b_n, n0, g.N, b_kfast, tid);
 
         double acc[TM][TN][CPLX ? 4 : 2];
 #pragma unroll
@@ -123,24 +164,26 @@ __global__ void __launch_bounds__(Cfg::NT) contract_dmma_kernel(ContractArgs g) 
 #pragma unroll
                 for (int e = 0; e < (CPLX ? 4 : 2); ++e) acc[i][j][e] = 0.0;
 
-        auto issue = [&](int64_t kit, int slot) {
+        // `fetch(kit)` loads the k offsets of iteration kit; `issue(slot)` starts its copies.
+        auto fetch = [&](int64_t kit) {
+            ga.prefetch(g.a_k, kit * BK, g.K, a_kfast, tid);
+            gb.prefetch(g.b_k, kit * BK, g.K, b_kfast, tid);
+        };
+        auto issue = [&](int slot) {
             char* sa = smem + (size_t)slot * Cfg::STAGE_BYTES;
             char* sb = sa + (size_t)Cfg::A_ELEMS * ES;
-            const int64_t k0 = kit * BK;
-            if (!CPLX && g.a_vec == 2)
-                gather_tile<Cfg, BM, Cfg::PM, 2>(sa, Ab, g.a_m, g.a_k, m0, g.M, k0, g.K, g.a_kfast, tid);
-            else
-                gather_tile<Cfg, BM, Cfg::PM, 1>(sa, Ab, g.a_m, g.a_k, m0, g.M, k0, g.K, g.a_kfast, tid);
-            if (!CPLX && g.b_vec == 2)
-                gather_tile<Cfg, BN, Cfg::PN, 2>(sb, Bb, g.b_n, g.b_k, n0, g.N, k0, g.K, g.b_kfast, tid);
-            else
-                gather_tile<Cfg, BN, Cfg::PN, 1>(sb, Bb, g.b_n, g.b_k, n0, g.N, k0, g.K, g.b_kfast, tid);
+            ga.issue(sa, Ab, a_kfast, tid);
+            gb.issue(sb, Bb, b_kfast, tid);
         };
 
         // Prologue: fill STAGES-1 slots.
+        fetch(kb);
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (kb + s < ke) issue(kb + s, s);
+            if (kb + s < ke) {
+                issue(s);
+                fetch(kb + s + 1);
+            }
             cp_async_commit();
         }
         int slot = 0;
@@ -151,49 +194,85 @@ __global__ void __launch_bounds__(Cfg::NT) contract_dmma_kernel(ContractArgs g) 
                 const int64_t nxt = kit + STAGES - 1;
                 int ns = slot + STAGES - 1;
                 if (ns >= STAGES) ns -= STAGES;
-                if (nxt < ke) issue(nxt, ns);
+                if (nxt < ke && !(g.debug & 1)) {
+                    issue(ns);
+                    if (!(g.debug & 2)) fetch(nxt + 1);
+                }
                 cp_async_commit();
             }
             const char* sa = smem + (size_t)slot * Cfg::STAGE_BYTES;
             const char* sb = sa + (size_t)Cfg::A_ELEMS * ES;
 #pragma unroll
-            for (int kk = 0; kk < BK; kk += 4) {
+            for (int kk = 0; kk < BK; kk += 8) {
+                // One m16n8k8 step: fragments of the two 8-row halves (h) and the two 4-deep
+                // k halves (q) of every m16 tile; the 8-column tiles of B likewise.
                 if (CPLX) {
-                    double ar[TM], ai[TM], nai[TM], br[TN], bi[TN];
-#pragma unroll
-                    for (int i = 0; i < TM; ++i) {
-                        double2 v = *reinterpret_cast<const double2*>(sa + (size_t)(a_frag + 8 * i * a_sm + kk * a_sk) * 16);
-                        ar[i] = v.x;
-                        ai[i] = g.conj_a ? -v.y : v.y;
-                        nai[i] = -ai[i];
-                    }
-#pragma unroll
-                    for (int j = 0; j < TN; ++j) {
-                        double2 v = *reinterpret_cast<const double2*>(sb + (size_t)(b_frag + 8 * j * b_sn + kk * b_sk) * 16);
-                        br[j] = v.x;
-                        bi[j] = g.conj_b ? -v.y : v.y;
-                    }
+                    double ar[TM][2], ai[TM][2], nai[TM][2], br[TN][2], bi[TN][2];
 #pragma unroll
                     for (int i = 0; i < TM; ++i)
 #pragma unroll
-                        for (int j = 0; j < TN; ++j) {
-                            dmma(acc[i][j][0], acc[i][j][1], ar[i], br[j]);
-                            dmma(acc[i][j][2], acc[i][j][3], ar[i], bi[j]);
-                            dmma(acc[i][j][0], acc[i][j][1], nai[i], bi[j]);
-                            dmma(acc[i][j][2], acc[i][j][3], ai[i], br[j]);
+                        for (int q = 0; q < 2; ++q) {
+                            double2 v = *reinterpret_cast<const double2*>(
+                                sa + (size_t)(a_frag + 8 * i * a_sm + (kk + 4 * q) * a_sk) * 16);
+                            ar[i][q] = v.x;
+                            ai[i][q] = g.conj_a ? -v.y : v.y;
+                            nai[i][q] = -ai[i][q];
                         }
-                } else {
-                    double af[TM], bf[TN];
-#pragma unroll
-                    for (int i = 0; i < TM; ++i)
-                        af[i] = *reinterpret_cast<const double*>(sa + (size_t)(a_frag + 8 * i * a_sm + kk * a_sk) * 8);
 #pragma unroll
                     for (int j = 0; j < TN; ++j)
-                        bf[j] = *reinterpret_cast<const double*>(sb + (size_t)(b_frag + 8 * j * b_sn + kk * b_sk) * 8);
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            double2 v = *reinterpret_cast<const double2*>(
+                                sb + (size_t)(b_frag + 8 * j * b_sn + (kk + 4 * q) * b_sk) * 16);
+                            br[j][q] = v.x;
+                            bi[j][q] = g.conj_b ? -v.y : v.y;
+                        }
+                    // Four passes over the warp tile; the two updates of one accumulator are
+                    // (TM / 2) * TN * 2 instructions apart.
+#pragma unroll
+                    for (int i = 0; i < TM; i += 2)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j)
+                            dmma16(acc[i][j][0], acc[i][j][1], acc[i + 1][j][0], acc[i + 1][j][1], ar[i][0], ar[i + 1][0],
+                                   ar[i][1], ar[i + 1][1], br[j][0], br[j][1]);
+#pragma unroll
+                    for (int i = 0; i < TM; i += 2)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j)
+                            dmma16(acc[i][j][2], acc[i][j][3], acc[i + 1][j][2], acc[i + 1][j][3], ar[i][0], ar[i + 1][0],
+                                   ar[i][1], ar[i + 1][1], bi[j][0], bi[j][1]);
+#pragma unroll
+                    for (int i = 0; i < TM; i += 2)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j)
+                            dmma16(acc[i][j][0], acc[i][j][1], acc[i + 1][j][0], acc[i + 1][j][1], nai[i][0], nai[i + 1][0],
+                                   nai[i][1], nai[i + 1][1], bi[j][0], bi[j][1]);
+#pragma unroll
+                    for (int i = 0; i < TM; i += 2)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j)
+                            dmma16(acc[i][j][2], acc[i][j][3], acc[i + 1][j][2], acc[i + 1][j][3], ai[i][0], ai[i + 1][0],
+                                   ai[i][1], ai[i + 1][1], br[j][0], br[j][1]);
+                } else {
+                    double af[TM][2], bf[TN][2];
 #pragma unroll
                     for (int i = 0; i < TM; ++i)
 #pragma unroll
-                        for (int j = 0; j < TN; ++j) dmma(acc[i][j][0], acc[i][j][1], af[i], bf[j]);
+                        for (int q = 0; q < 2; ++q)
+                            af[i][q] = *reinterpret_cast<const double*>(
+                                sa + (size_t)(a_frag + 8 * i * a_sm + (kk + 4 * q) * a_sk) * 8);
+#pragma unroll
+                    for (int j = 0; j < TN; ++j)
+#pragma unroll
+                        for (int q = 0; q < 2; ++q)
+                            bf[j][q] = *reinterpret_cast<const double*>(
+                                sb + (size_t)(b_frag + 8 * j * b_sn + (kk + 4 * q) * b_sk) * 8);
+#pragma unroll
+                    for (int i = 0; i < TM; i += 2)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j)
+                            dmma16(acc[i][j][0], acc[i][j][1], acc[i + 1][j][0], acc[i + 1][j][1], af[i][0], af[i + 1][0],
+                                   af[i][1], af[i + 1][1], bf[j][0], bf[j][1]);
                 }
             }
             if (++slot == STAGES) slot = 0;
@@ -259,7 +338,27 @@ __global__ void __launch_bounds__(Cfg::NT) contract_dmma_kernel(ContractArgs g) 
     }
 }
 
+template <typename Cfg>
+__global__ void __launch_bounds__(Cfg::NT, 1) contract_dmma_kernel(ContractArgs g) {
+    extern __shared__ __align__(16) char smem[];
+    const int64_t it_begin = (int64_t)blockIdx.x * g.iters_per_cta;
+    const int64_t it_end = min(g.total_iters, it_begin + g.iters_per_cta);
+    if (Cfg::kCplx) {
+        dmma_range<Cfg, 1, 1>(g, smem, it_begin, it_end);
+    } else if (g.a_vec == 2 && g.b_vec == 2) {
+        dmma_range<Cfg, 2, 2>(g, smem, it_begin, it_end);
+    } else if (g.a_vec == 2) {
+        dmma_range<Cfg, 2, 1>(g, smem, it_begin, it_end);
+    } else if (g.b_vec == 2) {
+        dmma_range<Cfg, 1, 2>(g, smem, it_begin, it_end);
+    } else {
+        dmma_range<Cfg, 1, 1>(g, smem, it_begin, it_end);
+    }
+}
+
 // Adds the scratch slots of every cut tile in CTA order and applies alpha/beta.
+// Grid: (tiles, kFixSplit); each CTA owns one slice of a tile's elements.
+constexpr int kFixSplit = 4;
 template <typename Cfg>
 __global__ void __launch_bounds__(256) contract_dmma_fixup_kernel(ContractArgs g) {
     constexpr bool CPLX = Cfg::kCplx;
@@ -275,7 +374,8 @@ __global__ void __launch_bounds__(256) contract_dmma_fixup_kernel(ContractArgs g
     const int64_t m0 = tm * BM, n0 = tn * BN;
     char* Cb = g.c + g.c_b[bb] * (int64_t)ES;
     const bool read_c = g.beta_re != 0.0 || g.beta_im != 0.0;
-    for (int idx = threadIdx.x; idx < BM * BN; idx += blockDim.x) {
+    constexpr int SLICE = BM * BN / kFixSplit;
+    for (int idx = blockIdx.y * SLICE + threadIdx.x; idx < (blockIdx.y + 1) * SLICE; idx += blockDim.x) {
         const int ml = idx % BM, nl = idx / BM;
         if (m0 + ml >= g.M || n0 + nl >= g.N) continue;
         double sr = 0.0, si = 0.0;
@@ -320,6 +420,8 @@ static tfb_status run_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractArgs a
         if (it == occupancy.end()) {
             TFB_CUDA(cudaFuncSetAttribute(contract_dmma_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           Cfg::SMEM_BYTES));
+            TFB_CUDA(cudaFuncSetAttribute(contract_dmma_kernel<Cfg>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
             TFB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, contract_dmma_kernel<Cfg>, Cfg::NT,
                                                                    Cfg::SMEM_BYTES));
             if (occ < 1) return fail(TFB_ERR_DEVICE, "DMMA kernel does not fit on an SM");
@@ -351,10 +453,14 @@ static tfb_status run_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractArgs a
         TFB_TRY(ws.alloc(ctx, (size_t)grid * 2 * Cfg::TILE_ELEMS * Cfg::ES));
         a.partial = (char*)ws.ptr;
     }
-    contract_dmma_kernel<Cfg><<<(unsigned)grid, Cfg::NT, Cfg::SMEM_BYTES, ctx->stream>>>(a);
+    {
+        LaunchScope ls(ctx, "contract_dmma");
+        contract_dmma_kernel<Cfg><<<(unsigned)grid, Cfg::NT, Cfg::SMEM_BYTES, ctx->stream>>>(a);
+    }
     TFB_CUDA(cudaGetLastError());
     if (cuts) {
-        contract_dmma_fixup_kernel<Cfg><<<(unsigned)a.n_tiles, 256, 0, ctx->stream>>>(a);
+        LaunchScope ls(ctx, "contract_dmma_fixup");
+        contract_dmma_fixup_kernel<Cfg><<<dim3((unsigned)a.n_tiles, kFixSplit), 256, 0, ctx->stream>>>(a);
         TFB_CUDA(cudaGetLastError());
     }
     (void)p;
@@ -362,8 +468,9 @@ static tfb_status run_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractArgs a
 }
 
 using RealBig = DmmaCfg<false, 128, 128, 16, 4, 4, 3>;
+using RealBig8 = DmmaCfg<false, 128, 128, 16, 2, 4, 3>;
 using RealSmall = DmmaCfg<false, 64, 64, 16, 2, 2, 4>;
-using CplxMain = DmmaCfg<true, 64, 64, 8, 2, 4, 4>;
+using CplxMain = DmmaCfg<true, 64, 64, 16, 4, 4, 4>;
 using CplxSmall = DmmaCfg<true, 32, 32, 8, 2, 2, 4>;
 
 tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
@@ -376,11 +483,13 @@ tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined)
     TFB_TRY(get_tables(ctx, p, &t));
     ContractArgs a;
     fill_args(p, *t, &a);
+    a.debug = env_int("TFB_DEBUG_SKIP", 0);
     const int shape = env_int("TFB_DMMA_TILE", 0);  // 0 auto, 1 small, 2 big
     if (p.dtype == TFB_F64) {
         bool small = (a.M <= 64 || a.N <= 64 || a.M * a.N * a.B < (int64_t)128 * 128 * ctx->sm_count / 2);
         if (shape == 1) small = true;
         if (shape == 2) small = false;
+        if (shape == 3) return run_cfg<RealBig8>(ctx, p, a);
         return small ? run_cfg<RealSmall>(ctx, p, a) : run_cfg<RealBig>(ctx, p, a);
     }
     bool small = (a.M <= 32 || a.N <= 32);

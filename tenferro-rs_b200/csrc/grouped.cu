@@ -136,6 +136,7 @@ tfb_status grouped_simt(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_proble
     g.total_tiles = total;
     g.alpha_re = alpha.re; g.alpha_im = alpha.im; g.beta_re = beta.re; g.beta_im = beta.im;
     const int grid = (int)std::min<int64_t>(total, (int64_t)ctx->sm_count * 16);
+    LaunchScope ls(ctx, "grouped_simt");
     switch (dtype) {
         case TFB_F32: grouped_simt_kernel<float><<<grid, 64, 0, ctx->stream>>>(g); break;
         case TFB_F64: grouped_simt_kernel<double><<<grid, 64, 0, ctx->stream>>>(g); break;

@@ -255,7 +255,7 @@ tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labe
         LoopNest nest;
         TFB_TRY(make_nest(all, &nest));
         if (used) *used = "elementwise_mul";
-        return launch_elementwise_mul(ctx, dtype, nest, a.ptr, b.ptr, c.ptr, alpha, beta, a.conj, b.conj);
+        return launch_elementwise_mul(ctx, dtype, nest, p.a, p.b, p.c, alpha, beta, p.conj_a, p.conj_b);
     }
     return launch_contract(ctx, p, force_kernel, used);
 }

@@ -142,6 +142,7 @@ static tfb_status permute_typed(tfb_ctx* ctx, const LoopNest& nest_out_order, co
         int64_t cap = (int64_t)sms * 16;
         int grid = (int)(blocks < cap ? blocks : cap);
         if (grid < 1) grid = 1;
+        LaunchScope ls(ctx, "permute_rows");
         if (vec)
             permute_rows_kernel<T, VMAX><<<grid, 256, 0, ctx->stream>>>(nest, (const T*)in, (T*)out, ep);
         else
@@ -176,6 +177,7 @@ static tfb_status permute_typed(tfb_ctx* ctx, const LoopNest& nest_out_order, co
             int64_t n_tiles = ti * tj * rest;
             int64_t cap = (int64_t)sms * 32;
             int grid = (int)(n_tiles < cap ? n_tiles : cap);
+            LaunchScope ls(ctx, "permute_tiled");
             permute_tiled_kernel<T><<<grid, 256, 0, ctx->stream>>>(r, (const T*)in, (T*)out, ep, ti, tj, n_tiles);
             TFB_CUDA(cudaGetLastError());
             return TFB_OK;
@@ -184,6 +186,7 @@ static tfb_status permute_typed(tfb_ctx* ctx, const LoopNest& nest_out_order, co
     int64_t blocks = (nest.total + 255) / 256;
     int64_t cap = (int64_t)sms * 16;
     int grid = (int)(blocks < cap ? blocks : cap);
+    LaunchScope ls(ctx, "permute_generic");
     permute_generic_kernel<T><<<grid, 256, 0, ctx->stream>>>(nest, (const T*)in, (T*)out, ep);
     TFB_CUDA(cudaGetLastError());
     return TFB_OK;
@@ -217,6 +220,7 @@ static tfb_status scale_typed(tfb_ctx* ctx, const LoopNest& nest, void* out, Sca
     int64_t blocks = (nest.total + 255) / 256;
     int64_t cap = (int64_t)ctx->sm_count * 16;
     int grid = (int)(blocks < cap ? blocks : cap);
+    LaunchScope ls(ctx, "scale");
     scale_kernel<T><<<grid, 256, 0, ctx->stream>>>(nest, (T*)out, Ops<T>::from(beta), beta.is_zero());
     TFB_CUDA(cudaGetLastError());
     return TFB_OK;
@@ -254,6 +258,7 @@ static tfb_status ewmul_typed(tfb_ctx* ctx, const LoopNest& nest, const void* a,
     int64_t blocks = (nest.total + 255) / 256;
     int64_t cap = (int64_t)ctx->sm_count * 16;
     int grid = (int)(blocks < cap ? blocks : cap);
+    LaunchScope ls(ctx, "elementwise_mul");
     ewmul_kernel<T><<<grid, 256, 0, ctx->stream>>>(nest, (const T*)a, (const T*)b, (T*)out, ep, ca, cb);
     TFB_CUDA(cudaGetLastError());
     return TFB_OK;
@@ -410,15 +415,19 @@ static tfb_status reduce_typed(tfb_ctx* ctx, const LoopNest& kept, const LoopNes
         TFB_TRY(ws.alloc(ctx, sizeof(T) * (size_t)splits * (size_t)kept.total));
         partial = (T*)ws.ptr;
     }
+    {
+    LaunchScope ls(ctx, "reduce");
     if (lanes_on_red)
         reduce_kernel<T, OP, true><<<grid, 256, 0, ctx->stream>>>(kept, red, (const T*)in, (T*)out, partial, splits, ep);
     else
         reduce_kernel<T, OP, false><<<grid, 256, 0, ctx->stream>>>(kept, red, (const T*)in, (T*)out, partial, splits,
                                                                    ep);
+    }
     TFB_CUDA(cudaGetLastError());
     if (splits > 1) {
         int64_t blocks = (kept.total + 255) / 256;
         int g2 = (int)(blocks < (int64_t)sms * 8 ? blocks : (int64_t)sms * 8);
+        LaunchScope ls(ctx, "reduce_finish");
         reduce_finish_kernel<T, OP><<<g2, 256, 0, ctx->stream>>>(kept, partial, (T*)out, splits, ep);
         TFB_CUDA(cudaGetLastError());
     }

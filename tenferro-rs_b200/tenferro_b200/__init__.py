@@ -21,6 +21,7 @@ from .device import (  # noqa: F401
 )
 from .einsum import (  # noqa: F401
     ContractionTree,
+    PreparedEinsum,
     Subscripts,
     einsum,
     einsum_into,

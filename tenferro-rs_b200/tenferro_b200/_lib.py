@@ -85,6 +85,12 @@ PROTOTYPES = {
     "tfb_memset_async": (C.c_int, [_VP, _VP, C.c_int, C.c_size_t]),
     "tfb_host_alloc": (C.c_int, [C.c_size_t, _VPP]),
     "tfb_host_free": (C.c_int, [_VP]),
+    "tfb_kernel_launch_count": (C.c_ulonglong, []),
+    "tfb_ctx_profile_begin": (C.c_int, [_VP]),
+    "tfb_ctx_profile_read": (C.c_int, [_VP, C.c_char_p, c_size_p, C.POINTER(C.c_double)]),
+    "tfb_ctx_profile_end": (C.c_int, [_VP]),
+    "tfb_probe_fp64_tflops": (C.c_int, [_VP, C.POINTER(C.c_double)]),
+    "tfb_probe_hbm_gbs": (C.c_int, [_VP, C.POINTER(C.c_double)]),
     "tfb_event_record": (C.c_int, [_VP, _VPP]),
     "tfb_event_wait": (C.c_int, [_VP, _VP]),
     "tfb_event_synchronize": (C.c_int, [_VP]),

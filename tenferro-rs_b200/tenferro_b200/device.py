@@ -177,6 +177,17 @@ class Context:
     def memset(self, dst: int, value: int, nbytes: int) -> None:
         check(lib.tfb_memset_async(self.handle, C.c_void_p(dst), value, nbytes))
 
+    @staticmethod
+    def host_alloc(nbytes: int) -> int:
+        """Page-locked host memory (for asynchronous transfers)."""
+        p = C.c_void_p()
+        check(lib.tfb_host_alloc(nbytes, C.byref(p)))
+        return p.value or 0
+
+    @staticmethod
+    def host_free(ptr: int) -> None:
+        check(lib.tfb_host_free(C.c_void_p(ptr)))
+
     def pool_stats(self):
         r, u = C.c_size_t(), C.c_size_t()
         check(lib.tfb_pool_stats(self.handle, C.byref(r), C.byref(u)))
@@ -199,6 +210,33 @@ class Context:
         sm, mem, major, minor = C.c_int(), C.c_size_t(), C.c_int(), C.c_int()
         check(lib.tfb_ctx_properties(self.handle, C.byref(sm), C.byref(mem), C.byref(major), C.byref(minor)))
         return {"sm_count": sm.value, "total_mem": mem.value, "cc": (major.value, minor.value)}
+
+    # -- measurement
+    def profile_begin(self) -> None:
+        check(lib.tfb_ctx_profile_begin(self.handle))
+
+    def profile_read(self, kernel: str):
+        """(launches, total device ms) of one kernel family since profile_begin()."""
+        n, ms = C.c_size_t(), C.c_double()
+        check(lib.tfb_ctx_profile_read(self.handle, kernel.encode(), C.byref(n), C.byref(ms)))
+        return n.value, ms.value
+
+    def profile_end(self) -> None:
+        check(lib.tfb_ctx_profile_end(self.handle))
+
+    def probe_fp64_tflops(self) -> float:
+        v = C.c_double()
+        check(lib.tfb_probe_fp64_tflops(self.handle, C.byref(v)))
+        return v.value
+
+    def probe_hbm_gbs(self) -> float:
+        v = C.c_double()
+        check(lib.tfb_probe_hbm_gbs(self.handle, C.byref(v)))
+        return v.value
+
+    @staticmethod
+    def kernel_launch_count() -> int:
+        return int(lib.tfb_kernel_launch_count())
 
     def record_event(self) -> "CompletionEvent":
         h = C.c_void_p()

@@ -163,6 +163,29 @@ def einsum_with_plan_into(tree: ContractionTree, operands: Sequence[Tensor], alp
     output.event = ctx.record_event()
 
 
+class PreparedEinsum:
+    """`einsum_with_plan_into` with the argument marshalling done once: for hot loops that
+    repeat one contraction on the same buffers (tenferro-einsum/src/lib.rs:124-144).  `run`
+    only enqueues; it records no event (use `ctx.record_event()` when one is needed)."""
+
+    def __init__(self, tree: ContractionTree, operands: Sequence[Tensor], output: Tensor, alpha=1.0, beta=0.0):
+        self.ctx = _select_context(operands, output)
+        self.tree, self.operands, self.output = tree, list(operands), output
+        dtype = output.dtype
+        for t in operands:
+            if t.dtype != dtype:
+                raise InvalidArgument(f"operand dtype {t.dtype} differs from the output's {dtype}")
+        self._keep: list = []
+        self._views = (_lib.TfbView * max(len(operands), 1))(*[t.as_operand_view(self._keep) for t in operands])
+        self._out = output.as_operand_view(self._keep)
+        self._alpha, self._beta = scalar_arg(alpha, dtype), scalar_arg(beta, dtype)
+        self._code = dtype_code(dtype)
+
+    def run(self) -> None:
+        check(lib.tfb_einsum_with_plan_into(self.ctx.handle, self.tree.handle, self._code, len(self.operands),
+                                            self._views, self._alpha, self._beta, C.byref(self._out)))
+
+
 def einsum_with_plan(tree: ContractionTree, operands: Sequence[Tensor]) -> Tensor:
     """tenferro-einsum/src/lib.rs:415-430."""
     if not operands:

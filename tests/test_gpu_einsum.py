@@ -276,11 +276,11 @@ def test_permute_set_bit_exact(tb, dtype, shape, perm):
     got = t.permute(perm).contiguous(tb.MemoryOrder.ColumnMajor)
     want = np.transpose(a, perm).copy()
     assert got.strides()[0] == 1
-    assert np.array_equal(got.to_numpy().view(np.uint8), np.asfortranarray(want).view(np.uint8))
+    assert got.to_numpy().tobytes(order="F") == want.tobytes(order="F")
     # permuting back restores every bit (a size-independent property used at full size too)
     inv = np.argsort(perm)
     back = got.permute(list(inv)).contiguous(tb.MemoryOrder.ColumnMajor)
-    assert np.array_equal(back.to_numpy().view(np.uint8), np.asfortranarray(a).view(np.uint8))
+    assert back.to_numpy().tobytes(order="F") == a.tobytes(order="F")
 
 
 def test_reduce_set(tb, oracle):
