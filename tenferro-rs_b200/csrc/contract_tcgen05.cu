@@ -1,8 +1,496 @@
-// f32 / Complex32 contraction on the 5th-generation tensor cores (placeholder: declines).
-#include "common.h"
+// f32 contraction on the 5th-generation tensor cores: TMA -> swizzled shared memory ->
+// 3xTF32 split -> tcgen05.mma (kind::tf32) into a TMEM accumulator -> epilogue.
+//
+// One CTA computes one 128 x BN tile of C (BN = 256 or 128).  Warp roles:
+//   warp 0      TMA producer: one thread issues cp.async.bulk.tensor loads of the raw f32
+//               operand tiles straight from the strided tensors (the "permute" of
+//               permute-into-GEMM is the tensor map), 128-byte swizzle, zero fill at the edges;
+//   warps 2-9   split every element a into big = tf32(a) (written back in place) and
+//               small = a - big (second tile, same swizzled position);
+//   warp 1      one thread issues, per 8-deep k step, the three products
+//               small*big, big*small, big*big into the same TMEM accumulator - f32 accuracy
+//               from TF32 tensor cores (the dropped small*small term is ~2^-22 relative);
+//   warps 2-9   promotion: every 4 k-blocks tcgen05.ld the finished work accumulator and add
+//               it to an f32 running sum in registers (two work accumulators alternate, so
+//               the tensor core never waits); epilogue: alpha/beta, store through the C
+//               offset tables (any output strides).
+// Stages cycle through mbarriers: full (TMA bytes landed) -> split (converters done) ->
+// empty (tcgen05.commit: the MMAs that read the stage have retired); work accumulators
+// through chunk_done (commit) -> promoted.  Every wait has an
+// iteration bound; when one expires the kernel records a status word, keeps going with
+// whatever data it has, frees its TMEM and returns - the host reports DeviceError.
+//
+// Operands may be K-major (contracted group has unit stride) or MN-major (free group has
+// unit stride); the instruction descriptor's major bits select the layout, so neither needs
+// a transpose pass.  Layouts TMA cannot describe (unit stride in neither group, strides that
+// are not multiples of 16 bytes, more than one non-fusable mode per group) are declined and
+// run on the SIMT kernel.
+//
+// Semantics: PrimDescriptor::{Contract, BatchedGemm}, tenferro-prims/src/lib.rs:156-168, 227-239.
+#include <cuda.h>
+
+#include "contract_common.cuh"
+#include "contract_tables.h"
+
 namespace tfb {
-tfb_status contract_tcgen05(tfb_ctx*, const ContractProblem&, bool* declined) {
-    *declined = true;
+
+namespace {
+
+constexpr int kBM = 128, kBK = 32;  // tile rows, k per stage (32 f32 = one 128-byte swizzle row)
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct TcArgs {
+    char* c;
+    const int64_t* c_b;
+    const int64_t* c_m;
+    const int64_t* c_n;
+    int64_t M, N, K, B;
+    float alpha, beta;
+    int a_mn_major, b_mn_major;  // 0: K-major tile, 1: MN-major tile
+    int64_t tiles_m, tiles_n;
+    int group_m;                 // m-tiles per raster group (L2 reuse)
+    int* status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit polls, leaving `code` in the status word.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try(bar, parity)) return;
+        // Once any wait of this launch has given up, the others stop waiting too.
+        if ((i & 1023u) == 1023u && *(volatile int*)status != 0) return;
+    }
+    atomicCAS(status, 0, code);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, sm_100 format: start address, leading and stride byte
+// offsets in 16-byte units, version 1 at bit 46, layout type at bits 61-63
+// (2: 128-byte swizzle of 16-byte units; 1: 128-byte swizzle of 32-byte units, the only
+// layout the tensor core accepts for MN-major 32-bit operands).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+           (1ull << 46) | ((uint64_t)layout << 61);
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+
+constexpr int kChunk = 4;           // k-blocks accumulated inside TMEM before promotion (K = 128)
+constexpr int kSplitThreads = 256;  // warps 2..9
+
+template <int BN>
+struct TcCfg {
+    static constexpr int A_BYTES = kBM * kBK * 4;  // 16 KB
+    static constexpr int B_BYTES = BN * kBK * 4;
+    static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);  // big + small of both operands
+    static constexpr int STAGES = BN == 256 ? 2 : 3;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+    static constexpr int TMEM_COLS = 2 * BN;  // two f32 work accumulators, one column per n each
+    static constexpr int COLS_PER_WARP = BN / 2;
+    static_assert(kChunk >= STAGES, "promotion lag assumes a chunk spans at least the ring");
+};
+
+// The tensor core adds into its f32 accumulator with truncation, which shrinks a running
+// sum by ~2^-26 per MMA: harmless for K of a few hundred, 4e-4 at K = 65536.  So TMEM only
+// ever holds the sum of kChunk k-blocks (48 MMAs); the split warps add each finished chunk
+// to an f32 running sum in registers with ordinary round-to-nearest adds while the MMA
+// thread fills the other work accumulator.
+template <int BN>
+__global__ void __launch_bounds__(64 + kSplitThreads, 1)
+contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
+    using Cfg = TcCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    constexpr int CPW = Cfg::COLS_PER_WARP;
+    extern __shared__ char smem_raw[];
+    // 128-byte swizzle atoms repeat every 1024 bytes: align the ring to that.
+    char* smem = (char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t ring = smem_u32(smem);
+    const uint32_t bars = ring + STAGES * Cfg::STAGE_BYTES;
+    // barrier layout: full[s], split[s], empty[s], chunk_done[2], promoted[2], then the TMEM base word
+    auto bar_full = [&](int s) { return bars + 8u * s; };
+    auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+    auto bar_chunk = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+    auto bar_promoted = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+    const uint32_t tmem_word = bars + 8u * (3 * STAGES + 4);
+    volatile uint32_t* tmem_word_ptr = (volatile uint32_t*)(smem + STAGES * Cfg::STAGE_BYTES + 8 * (3 * STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // Tile of this CTA: m-tiles are visited in groups so that CTAs running together share
+    // B panels (and the A panels of the group) through L2.
+    int64_t tile = blockIdx.x;
+    const int64_t tiles_per_batch = g.tiles_m * g.tiles_n;
+    const int64_t bb = tile / tiles_per_batch;
+    tile -= bb * tiles_per_batch;
+    const int64_t group_sz = (int64_t)g.group_m * g.tiles_n;
+    const int64_t grp = tile / group_sz;
+    const int64_t first_m = grp * g.group_m;
+    const int64_t rows_in_group = min((int64_t)g.group_m, g.tiles_m - first_m);
+    const int64_t in_grp = tile - grp * group_sz;
+    const int64_t tm = first_m + in_grp % rows_in_group;
+    const int64_t tn = in_grp / rows_in_group;
+    const int m0 = (int)(tm * kBM), n0 = (int)(tn * BN);
+    const int num_kb = (int)((g.K + kBK - 1) / kBK);
+    const int num_chunks = (num_kb + kChunk - 1) / kChunk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_split(s), kSplitThreads);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_chunk(b), 1);
+            mbar_init(bar_promoted(b), kSplitThreads);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_word, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_word_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t use = kb / STAGES;
+                mbar_wait(bar_empty(s), (use & 1) ^ 1, g.status, 0x101);
+                const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
+                const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+                mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
+                const int k0 = kb * kBK;
+                if (g.a_mn_major) {
+                    // [32 k][32 m] boxes, one per 32 rows of the tile
+                    for (int c = 0; c < kBM / 32; ++c)
+                        tma_load_3d(a_dst + c * 4096, &map_a, bar_full(s), m0 + 32 * c, k0, (int)bb);
+                } else {
+                    tma_load_3d(a_dst, &map_a, bar_full(s), k0, m0, (int)bb);
+                }
+                if (g.b_mn_major) {
+                    for (int c = 0; c < BN / 32; ++c)
+                        tma_load_3d(b_dst + c * 4096, &map_b, bar_full(s), n0 + 32 * c, k0, (int)bb);
+                } else {
+                    // box rows are capped at 256 by the hardware; BN <= 256
+                    tma_load_3d(b_dst, &map_b, bar_full(s), k0, n0, (int)bb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)g.a_mn_major << 15) |
+                                   ((uint32_t)g.b_mn_major << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            // K-major: rows of 128 bytes, 8-row atoms 1024 bytes apart; a k step moves 32 bytes
+            // inside the row.  MN-major: [32 k][32 mn] blocks 4096 bytes apart (leading offset),
+            // swizzle atoms of 4 k-rows 512 bytes apart (stride offset); a k step of 8 moves 1024 bytes.
+            const uint32_t a_lbo = g.a_mn_major ? 4096u : 16u, b_lbo = g.b_mn_major ? 4096u : 16u;
+            const uint32_t a_sbo = g.a_mn_major ? 512u : 1024u, b_sbo = g.b_mn_major ? 512u : 1024u;
+            const uint32_t a_lay = g.a_mn_major ? 1u : 2u, b_lay = g.b_mn_major ? 1u : 2u;
+            const uint32_t a_step = g.a_mn_major ? 1024u : 32u, b_step = g.b_mn_major ? 1024u : 32u;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t use = kb / STAGES;
+                const int chunk = kb / kChunk, buf = chunk & 1;
+                const bool chunk_first = kb % kChunk == 0;
+                const bool chunk_last = (kb % kChunk == kChunk - 1) || kb == num_kb - 1;
+                if (chunk_first && chunk >= 2) {
+                    // the work accumulator is free once the chunk it held has been promoted
+                    mbar_wait(bar_promoted(buf), ((uint32_t)(chunk >> 1) - 1) & 1, g.status, 0x105);
+                    tc_fence_after();
+                }
+                mbar_wait(bar_split(s), use & 1, g.status, 0x102);
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t a_big = ring + s * Cfg::STAGE_BYTES;
+                const uint32_t b_big = a_big + Cfg::A_BYTES;
+                const uint32_t a_small = b_big + Cfg::B_BYTES;
+                const uint32_t b_small = a_small + Cfg::A_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < kBK / 8; ++ks) {
+                    const uint64_t da_big = smem_desc(a_big + ks * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t da_small = smem_desc(a_small + ks * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t db_big = smem_desc(b_big + ks * b_step, b_lbo, b_sbo, b_lay);
+                    const uint64_t db_small = smem_desc(b_small + ks * b_step, b_lbo, b_sbo, b_lay);
+                    tc_mma_tf32(tmem_d, da_small, db_big, idesc, !(chunk_first && ks == 0));
+                    tc_mma_tf32(tmem_d, da_big, db_small, idesc, 1);
+                    tc_mma_tf32(tmem_d, da_big, db_big, idesc, 1);
+                }
+                tc_commit(bar_empty(s));                  // stage reusable once these MMAs have read it
+                if (chunk_last) tc_commit(bar_chunk(buf));  // work accumulator complete
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- split + promote, then epilogue
+        const int t = threadIdx.x - 64;  // 0..255
+        // warp w may touch TMEM lanes 32 * (w % 4) .. + 31; lane = row of the tile.  Warps 2-5
+        // own the first half of the columns, warps 6-9 the second.
+        const int lane_grp = warp & 3;
+        const int col0 = ((warp - 2) >> 2) * CPW;
+        const uint32_t tmem_mine = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)col0;
+        float acc[CPW];
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) acc[j] = 0.f;
+        int next_promote = 0;
+        auto promote = [&](int chunk) {
+            const int buf = chunk & 1;
+            mbar_wait(bar_chunk(buf), (uint32_t)(chunk >> 1) & 1, g.status, 0x104);
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < CPW; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_mine + (uint32_t)(buf * BN + c0), r);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            mbar_arrive(bar_promoted(buf));
+        };
+        for (int kb = 0; kb < num_kb; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t use = kb / STAGES;
+            mbar_wait(bar_full(s), use & 1, g.status, 0x103);
+            char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
+            char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
+            constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
+#pragma unroll 4
+            for (int c = t; c < CHUNKS; c += kSplitThreads) {
+                float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
+                float4 b, sm;
+                b.x = to_tf32(v.x); b.y = to_tf32(v.y); b.z = to_tf32(v.z); b.w = to_tf32(v.w);
+                sm.x = v.x - b.x; sm.y = v.y - b.y; sm.z = v.z - b.z; sm.w = v.w - b.w;
+                *reinterpret_cast<float4*>(big + (size_t)c * 16) = b;
+                *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
+            }
+            fence_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+            mbar_arrive(bar_split(s));
+            // A chunk whose last k-block lies STAGES behind has certainly retired: the stage
+            // just split could only be loaded after that k-block's MMAs freed it.
+            while (next_promote < num_chunks &&
+                   min((next_promote + 1) * kChunk, num_kb) - 1 + STAGES <= kb)
+                promote(next_promote++);
+        }
+        while (next_promote < num_chunks) promote(next_promote++);
+
+        const int row = lane_grp * 32 + lane;
+        const int64_t m = (int64_t)m0 + row;
+        if (m < g.M) {
+            float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
+            const int64_t cm = g.c_m[m];
+            const bool read_c = g.beta != 0.f;
+#pragma unroll
+            for (int j = 0; j < CPW; ++j) {
+                const int64_t n = (int64_t)n0 + col0 + j;
+                if (n < g.N) {
+                    float* p = C + cm + g.c_n[n];
+                    float v = g.alpha * acc[j];
+                    if (read_c) v += g.beta * *p;
+                    *p = v;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// One operand as TMA sees it: a (rows x K) matrix per batch entry with one unit-stride side.
+struct OperandMap {
+    bool ok = false;
+    bool mn_major = false;
+    CUtensorMap map;
+};
+
+// `free` = the M (or N) group, `k` = the contracted group, tns = tensor index (0: A, 1: B).
+OperandMap make_operand_map(const ContractProblem& p, const std::vector<Mode>& free, int tns, const void* base,
+                            int free_box_rows) {
+    OperandMap out;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return out;
+    if (free.size() > 1 || p.k.size() != 1 || p.batch.size() > 1) return out;
+    const int64_t rows = free.empty() ? 1 : free[0].extent, rs = free.empty() ? 0 : free[0].s[tns];
+    const int64_t K = p.k[0].extent, ks = p.k[0].s[tns];
+    const int64_t B = p.batch.empty() ? 1 : p.batch[0].extent, bs = p.batch.empty() ? 0 : p.batch[0].s[tns];
+    if ((uintptr_t)base % 16 != 0) return out;
+    cuuint64_t dims[3], strides[2];
+    cuuint32_t box[3], estr[3] = {1, 1, 1};
+    auto stride_ok = [](int64_t s) { return s > 0 && (s * 4) % 16 == 0; };
+    // A size-1 dimension has no meaningful stride; give it a legal one.
+    const int64_t batch_stride = (B > 1) ? bs : std::max<int64_t>(rows, 1) * std::max<int64_t>(K, 1);
+    if (ks == 1 && (rows == 1 || stride_ok(rs))) {
+        out.mn_major = false;
+        dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows; dims[2] = (cuuint64_t)B;
+        strides[0] = (cuuint64_t)((rows == 1 ? ((K + 3) / 4 * 4) : rs) * 4);
+        box[0] = kBK; box[1] = (cuuint32_t)free_box_rows; box[2] = 1;
+    } else if (rs == 1 && rows > 1 && (K == 1 || stride_ok(ks))) {
+        out.mn_major = true;
+        dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)B;
+        strides[0] = (cuuint64_t)((K == 1 ? ((rows + 3) / 4 * 4) : ks) * 4);
+        box[0] = 32; box[1] = kBK; box[2] = 1;
+    } else {
+        return out;
+    }
+    if (B > 1 && !stride_ok(bs)) return out;
+    strides[1] = (cuuint64_t)(((B > 1) ? bs : ((batch_stride + 3) / 4 * 4)) * 4);
+    if (strides[0] % 16 != 0 || strides[1] % 16 != 0) return out;
+    if (strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return out;
+    CUresult r = enc(&out.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     out.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    out.ok = (r == CUDA_SUCCESS);
+    return out;
+}
+
+template <int BN>
+tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcArgs g) {
+    using Cfg = TcCfg<BN>;
+    static std::mutex mu;
+    static std::map<int, bool> configured;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[ctx->device]) {
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg::SMEM_BYTES));
+            configured[ctx->device] = true;
+        }
+    }
+    g.tiles_m = (g.M + kBM - 1) / kBM;
+    g.tiles_n = (g.N + BN - 1) / BN;
+    g.group_m = 16;
+    const int64_t grid = g.tiles_m * g.tiles_n * g.B;
+    if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
+    LaunchScope ls(ctx, "contract_tf32x3");
+    contract_tf32x3_kernel<BN><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+    TFB_CUDA(cudaGetLastError());
     return TFB_OK;
 }
+
+}  // namespace
+
+tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
+    *declined = true;
+    if (p.dtype != TFB_F32) return TFB_OK;
+    if (env_int("TFB_NO_TCGEN05", 0)) return TFB_OK;
+    const int64_t M = p.M(), N = p.N(), K = p.K();
+    // Small problems stay on the SIMT kernel: a 128-row tile would be mostly padding.
+    if (M < 32 || N < 32 || K < 8) return TFB_OK;
+    if (M > INT32_MAX - 256 || N > INT32_MAX - 256 || K > INT32_MAX - 64) return TFB_OK;
+    const int bn = (N >= 256 && env_int("TFB_TC_BN", 256) == 256) ? 256 : 128;
+    OperandMap a = make_operand_map(p, p.m, 0, p.a, kBM);
+    OperandMap b = make_operand_map(p, p.n, 1, p.b, bn);
+    if (!a.ok || !b.ok) return TFB_OK;
+    std::shared_ptr<ContractTables> t;
+    TFB_TRY(get_tables(ctx, p, &t));
+    TcArgs g;
+    memset(&g, 0, sizeof g);
+    g.c = (char*)p.c;
+    g.c_b = t->c_b; g.c_m = t->c_m; g.c_n = t->c_n;
+    g.M = M; g.N = N; g.K = K; g.B = p.B();
+    g.alpha = (float)p.alpha.re;
+    g.beta = (float)p.beta.re;
+    g.a_mn_major = a.mn_major;
+    g.b_mn_major = b.mn_major;
+    g.status = ctx->dev_status;
+    *declined = false;
+    return bn == 256 ? launch_tc<256>(ctx, a, b, g) : launch_tc<128>(ctx, a, b, g);
+}
+
 }  // namespace tfb
