@@ -249,6 +249,25 @@ tfb_status tfb_plan_force_kernel(tfb_plan* plan, int kernel);
 tfb_status tfb_execute(tfb_plan* plan, const void* alpha, size_t n_inputs, const tfb_view* inputs,
                        const void* beta, const tfb_view* output);
 
+/* Reduce without any device allocation.  No counterpart in the reference: it exists for
+ * callers that may not allocate on the device at the moment they call - an application
+ * whose own allocator owns all device memory, a latency-critical loop, a framework callback
+ * where allocation is forbidden.  Same result as a Reduce plan run through tfb_execute:
+ *   C[modes_c] = alpha * reduce_op(A[modes_a]) + beta * C[modes_c],  modes_c a subset of modes_a
+ * (tenferro-prims/src/lib.rs:170-180 gives the formula), but the partial results of a split
+ * reduction are kept in a fixed 4 MiB array inside the library instead of a pool block, and
+ * the call uses neither cudaMalloc/cudaFree nor the pool.
+ *  - Limit: the output may hold at most 2 MiB (elements x element size); larger outputs are
+ *    rejected with TFB_ERR_INVALID_ARGUMENT.  Labels must not repeat inside modes_a.
+ *  - The first call on each device looks up the array's device address (one
+ *    cudaGetSymbolAddress); make that first call before any stream capture begins.
+ *  - All calls share the one array.  Nothing in it needs to start at zero (every slot is
+ *    written before it is read), but two calls whose kernels overlap on the GPU - different
+ *    streams, different contexts of the same device - race on it; keep them ordered. */
+tfb_status tfb_reduce_static(tfb_ctx* ctx, int32_t dtype, int32_t reduce_op, const uint32_t* modes_a, size_t n_modes_a,
+                             const tfb_view* a, const uint32_t* modes_c, size_t n_modes_c, const tfb_view* c,
+                             const void* alpha, const void* beta);
+
 /* Grouped (ragged) matrix products in one persistent launch:
  *   C_p[m_p, n_p] = alpha * A_p[m_p, k_p] * B_p[k_p, n_p] + beta * C_p   for p in 0..n_problems.
  * `PrimDescriptor::BatchedGemm` covers uniform batches only

@@ -461,4 +461,162 @@ tfb_status launch_reduce(tfb_ctx* ctx, int dtype, int op, const LoopNest& kept, 
     return fail(TFB_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
 }
 
+// ------------------------------------------------------------------ reduce without allocation
+// Some callers must not allocate device memory when they call in: an application that has
+// handed all device memory to an allocator of its own, a latency-critical loop that cannot
+// afford the pool's occasional trip to the driver, a framework callback in which device
+// allocation is forbidden.  For them the split partials of the reduce kernel live in this
+// fixed array instead of a pool block.  Every GPU that loads the library carries these
+// 4 MiB until the process exits.
+constexpr size_t kStaticReduceBytes = (size_t)4 << 20;
+static __device__ __align__(256) unsigned char g_static_reduce_scratch[kStaticReduceBytes];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel
+// could use: the device address is asked for once per device, with that device current.
+static tfb_status static_reduce_scratch(tfb_ctx* ctx, void** out) {
+    static std::mutex mu;
+    static std::map<int, void*> by_device;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = by_device.find(ctx->device);
+    if (it != by_device.end()) {
+        *out = it->second;
+        return TFB_OK;
+    }
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_reduce_scratch);
+    if (e != cudaSuccess || !ptr)
+        return fail(TFB_ERR_DEVICE, "cudaGetSymbolAddress(static reduce scratch) failed on device %d: %s", ctx->device,
+                    cudaGetErrorString(e));
+    by_device[ctx->device] = ptr;
+    *out = ptr;
+    return TFB_OK;
+}
+
+template <typename T, int OP>
+static tfb_status reduce_static_typed(tfb_ctx* ctx, const LoopNest& kept, const LoopNest& red, const void* in, void* out,
+                                      Scalar alpha, Scalar beta, bool conj, void* scratch) {
+    EpilogueArgs<T> ep = EpilogueArgs<T>::make(alpha, beta, conj);
+    auto min_stride = [](const LoopNest& n) {
+        int64_t m = INT64_MAX;
+        for (int d = 0; d < n.rank; ++d) {
+            int64_t s = n.stride[0][d] < 0 ? -n.stride[0][d] : n.stride[0][d];
+            if (n.extent[d] > 1 && s < m) m = s;
+        }
+        return m;
+    };
+    const bool lanes_on_red = kept.rank == 0 || min_stride(red) < min_stride(kept);
+    const int sms = ctx->sm_count;
+    const int64_t groups = lanes_on_red ? (kept.total + 7) / 8 : (kept.total + 255) / 256;
+    const int64_t target = (int64_t)sms * 8;
+    int64_t splits = 1;
+    if (groups < target) {
+        const int64_t want = target / (groups > 0 ? groups : 1);
+        const int64_t min_chunk = lanes_on_red ? 1024 : 64;
+        const int64_t max_splits = (red.total + min_chunk - 1) / min_chunk;
+        splits = want < max_splits ? want : max_splits;
+        // The partials have to fit the fixed array.
+        const int64_t fit = (int64_t)(kStaticReduceBytes / (sizeof(T) * (size_t)kept.total));
+        if (splits > fit) splits = fit;
+        if (splits > 1024) splits = 1024;
+        if (splits < 1) splits = 1;
+    }
+    int64_t gx = groups < target * 4 ? groups : target * 4;
+    if (gx < 1) gx = 1;
+    dim3 grid((unsigned)gx, (unsigned)splits);
+    T* partial = splits > 1 ? (T*)scratch : nullptr;
+    count_launch(1);
+    if (lanes_on_red)
+        reduce_kernel<T, OP, true><<<grid, 256, 0, ctx->stream>>>(kept, red, (const T*)in, (T*)out, partial, (int)splits, ep);
+    else
+        reduce_kernel<T, OP, false><<<grid, 256, 0, ctx->stream>>>(kept, red, (const T*)in, (T*)out, partial, (int)splits,
+                                                                   ep);
+    TFB_CUDA(cudaGetLastError());
+    if (splits > 1) {
+        const int64_t blocks = (kept.total + 255) / 256;
+        const int g2 = (int)(blocks < (int64_t)sms * 8 ? blocks : (int64_t)sms * 8);
+        count_launch(1);
+        reduce_finish_kernel<T, OP><<<g2, 256, 0, ctx->stream>>>(kept, partial, (T*)out, (int)splits, ep);
+        TFB_CUDA(cudaGetLastError());
+    }
+    return TFB_OK;
+}
+
+template <typename T>
+static tfb_status reduce_static_ops(tfb_ctx* ctx, int op, const LoopNest& kept, const LoopNest& red, const void* in,
+                                    void* out, Scalar alpha, Scalar beta, bool conj, void* scratch) {
+    switch (op) {
+        case TFB_REDUCE_SUM: return reduce_static_typed<T, TFB_REDUCE_SUM>(ctx, kept, red, in, out, alpha, beta, conj, scratch);
+        case TFB_REDUCE_MAX: return reduce_static_typed<T, TFB_REDUCE_MAX>(ctx, kept, red, in, out, alpha, beta, conj, scratch);
+        case TFB_REDUCE_MIN: return reduce_static_typed<T, TFB_REDUCE_MIN>(ctx, kept, red, in, out, alpha, beta, conj, scratch);
+    }
+    return fail(TFB_ERR_INVALID_ARGUMENT, "unknown reduce op %d", op);
+}
+
 }  // namespace tfb
+
+// See include/tenferro_b200.h.  The first call on a device looks up the scratch address
+// (cudaGetSymbolAddress); after that a call is two kernel launches and nothing else.
+extern "C" tfb_status tfb_reduce_static(tfb_ctx* ctx, int32_t dtype, int32_t reduce_op, const uint32_t* modes_a,
+                                        size_t n_modes_a, const tfb_view* a, const uint32_t* modes_c, size_t n_modes_c,
+                                        const tfb_view* c, const void* alpha, const void* beta) {
+    using namespace tfb;
+    if (!ctx || !a || !c || !alpha || !beta) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_reduce_static: NULL argument");
+    if (!dtype_valid(dtype)) return fail(TFB_ERR_INVALID_ARGUMENT, "unknown dtype %d", (int)dtype);
+    if (reduce_op < TFB_REDUCE_SUM || reduce_op > TFB_REDUCE_MIN)
+        return fail(TFB_ERR_INVALID_ARGUMENT, "unknown reduce op %d", (int)reduce_op);
+    if (reduce_op != TFB_REDUCE_SUM && dtype_is_complex(dtype))
+        return fail(TFB_ERR_INVALID_ARGUMENT, "Max/Min are undefined for complex types");
+    if (a->rank != n_modes_a) return fail(TFB_ERR_RANK_MISMATCH, "rank mismatch: expected %zu, got %zu (input)", n_modes_a, a->rank);
+    if (c->rank != n_modes_c) return fail(TFB_ERR_RANK_MISMATCH, "rank mismatch: expected %zu, got %zu (output)", n_modes_c, c->rank);
+    if ((n_modes_a && !modes_a) || (n_modes_c && !modes_c)) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_reduce_static: modes are NULL");
+    HView va, vc;
+    TFB_TRY(to_hview(*a, dtype, &va, "input"));
+    TFB_TRY(to_hview(*c, dtype, &vc, "output"));
+    if (vc.conj) return fail(TFB_ERR_INVALID_ARGUMENT, "the output view cannot carry the conjugate flag");
+    for (size_t i = 0; i < n_modes_a; ++i)
+        for (size_t j = i + 1; j < n_modes_a; ++j)
+            if (modes_a[i] == modes_a[j]) return fail(TFB_ERR_INVALID_ARGUMENT, "modes_a holds a repeated label");
+    std::vector<Mode> kept, red;
+    std::vector<bool> used(n_modes_a, false);
+    for (size_t i = 0; i < n_modes_c; ++i) {
+        size_t j = 0;
+        while (j < n_modes_a && modes_a[j] != modes_c[i]) ++j;
+        if (j == n_modes_a || used[j]) return fail(TFB_ERR_INVALID_ARGUMENT, "modes_c is not a subset of modes_a (label %u)", modes_c[i]);
+        if (va.dims[j] != vc.dims[i])
+            return fail(TFB_ERR_SHAPE_MISMATCH, "shape mismatch: expected [%lld], got [%lld] (label %u)", (long long)va.dims[j],
+                        (long long)vc.dims[i], modes_c[i]);
+        used[j] = true;
+        kept.push_back(Mode{va.dims[j], {va.strides[j], vc.strides[i], 0}});
+    }
+    for (size_t j = 0; j < n_modes_a; ++j)
+        if (!used[j]) red.push_back(Mode{va.dims[j], {va.strides[j], 0, 0}});
+    int64_t kept_total = 1, red_total = 1;
+    for (auto& m : kept) kept_total *= m.extent;
+    for (auto& m : red) red_total *= m.extent;
+    if (kept_total == 0) return TFB_OK;
+    if (red_total == 0) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_reduce_static: the reduced range is empty");
+    const size_t out_bytes = (size_t)kept_total * dtype_size(dtype);
+    if (out_bytes > kStaticReduceBytes / 2)
+        return fail(TFB_ERR_INVALID_ARGUMENT,
+                    "tfb_reduce_static: the output holds %zu bytes, more than the %zu this allocation-free entry point "
+                    "supports; use tfb_execute with a Reduce plan",
+                    out_bytes, kStaticReduceBytes / 2);
+    sort_and_fuse(kept, 1, 2);
+    sort_and_fuse(red, 0, 1);
+    LoopNest nk, nr;
+    TFB_TRY(make_nest(kept, &nk));
+    TFB_TRY(make_nest(red, &nr));
+    DeviceGuard guard(ctx->device);
+    void* scratch = nullptr;
+    TFB_TRY(static_reduce_scratch(ctx, &scratch));
+    const Scalar al = load_scalar(dtype, alpha), be = load_scalar(dtype, beta);
+    switch (dtype) {
+        case TFB_F32: return reduce_static_ops<float>(ctx, reduce_op, nk, nr, va.ptr, vc.ptr, al, be, va.conj, scratch);
+        case TFB_F64: return reduce_static_ops<double>(ctx, reduce_op, nk, nr, va.ptr, vc.ptr, al, be, va.conj, scratch);
+        case TFB_C32:
+            return reduce_static_typed<float2, TFB_REDUCE_SUM>(ctx, nk, nr, va.ptr, vc.ptr, al, be, va.conj, scratch);
+        case TFB_C64:
+            return reduce_static_typed<double2, TFB_REDUCE_SUM>(ctx, nk, nr, va.ptr, vc.ptr, al, be, va.conj, scratch);
+    }
+    return fail(TFB_ERR_INVALID_ARGUMENT, "unknown dtype %d", (int)dtype);
+}

@@ -107,6 +107,9 @@ PROTOTYPES = {
     "tfb_plan_kernel_name": (C.c_char_p, [_VP]),
     "tfb_plan_force_kernel": (C.c_int, [_VP, C.c_int]),
     "tfb_execute": (C.c_int, [_VP, _VP, C.c_size_t, C.POINTER(TfbView), _VP, C.POINTER(TfbView)]),
+    "tfb_reduce_static": (
+        C.c_int, [_VP, C.c_int32, C.c_int32, c_u32_p, C.c_size_t, C.POINTER(TfbView), c_u32_p, C.c_size_t,
+                  C.POINTER(TfbView), _VP, _VP]),
     "tfb_grouped_gemm": (C.c_int, [_VP, C.c_int32, C.c_size_t, C.POINTER(TfbGemmProblem), _VP, _VP]),
     "tfb_subscripts_new": (C.c_int, [C.c_size_t, c_size_p, C.POINTER(c_u32_p), C.c_size_t, c_u32_p, _VPP]),
     "tfb_subscripts_parse": (C.c_int, [C.c_char_p, _VPP]),

@@ -206,3 +206,18 @@ def grouped_gemm(problems, dtype, alpha=1.0, beta=0.0, ctx: Optional[Context] = 
         arr[i] = _lib.TfbGemmProblem(*p)
     check(lib.tfb_grouped_gemm(ctx.handle, dtype_code(dtype), len(problems), arr, scalar_arg(alpha, dtype),
                                scalar_arg(beta, dtype)))
+
+
+def reduce_static(modes_a, a: Tensor, modes_c, c: Tensor, op: ReduceOp = ReduceOp.Sum, alpha=1.0, beta=0.0,
+                  ctx: Optional[Context] = None) -> None:
+    """`c[modes_c] = alpha * op(a[modes_a]) + beta * c` through the entry point that allocates
+    nothing on the device (tfb_reduce_static): for callers that may not allocate when they call.
+    Outputs above 2 MiB are rejected; calls that overlap on the GPU race on the shared scratch."""
+    ctx = ctx or a.ctx
+    keep: list = []
+    va, vc = a.as_operand_view(keep), c.as_operand_view(keep)
+    ma = (C.c_uint32 * max(len(modes_a), 1))(*[int(m) for m in modes_a])
+    mc = (C.c_uint32 * max(len(modes_c), 1))(*[int(m) for m in modes_c])
+    check(lib.tfb_reduce_static(ctx.handle, dtype_code(c.dtype), int(op), ma, len(modes_a), C.byref(va), mc,
+                                len(modes_c), C.byref(vc), scalar_arg(alpha, c.dtype), scalar_arg(beta, c.dtype)))
+    c.event = ctx.record_event()
