@@ -204,6 +204,8 @@ tfb_status tfb_ctx_profile_read(tfb_ctx* ctx, const char* kernel, size_t* launch
 tfb_status tfb_ctx_profile_end(tfb_ctx* ctx);
 tfb_status tfb_probe_fp64_tflops(tfb_ctx* ctx, double* tflops);
 tfb_status tfb_probe_hbm_gbs(tfb_ctx* ctx, double* gbs);
+/* Dense TF32 rate of tcgen05.mma (128 x 256 x 8 tiles resident in shared memory), TFLOP/s. */
+tfb_status tfb_probe_tf32_tflops(tfb_ctx* ctx, double* tflops);
 
 /* CompletionEvent (tenferro-tensor/src/lib.rs:301-309, 677-713). */
 tfb_status tfb_event_record(tfb_ctx* ctx, tfb_event** out);    /* marks all work enqueued so far */

@@ -463,7 +463,77 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     return TFB_OK;
 }
 
+// Peak probe: one CTA per SM issues 128 x 256 x 8 TF32 MMAs back to back on operand tiles
+// that stay in shared memory; nothing else runs.  The quotient is the dense TF32 rate the
+// tensor pipe sustains, the denominator for "fraction of TF32 peak" (a 3xTF32 contraction
+// can reach a third of it in algorithmic flops).
+__global__ void __launch_bounds__(128, 1) probe_tf32_kernel(int iters, int* status) {
+    extern __shared__ char smem_raw[];
+    char* smem = (char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t base = smem_u32(smem);
+    const uint32_t a_tile = base, b_tile = base + 16384, bar = base + 16384 + 32768, tmem_word = bar + 8;
+    for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += blockDim.x) ((float*)smem)[i] = 1.0f;
+    fence_async_smem();
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_word, 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *(volatile uint32_t*)(smem + 16384 + 32768 + 8);
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc_mma_tf32(tmem_d, smem_desc(a_tile + ks * 32, 16, 1024, 2), smem_desc(b_tile + ks * 32, 16, 1024, 2),
+                            idesc, (it | ks) != 0);
+        }
+        tc_commit(bar);
+        mbar_wait(bar, 0, status, 0x201);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_d, 256);
+    }
+}
+
 }  // namespace
+
+extern "C" tfb_status tfb_probe_tf32_tflops(tfb_ctx* ctx, double* tflops) {
+    if (!ctx || !tflops) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_probe_tf32_tflops: NULL argument");
+    DeviceGuard g(ctx->device);
+    const int smem = 16384 + 32768 + 64 + 1024;
+    TFB_CUDA(cudaFuncSetAttribute(probe_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    cudaEvent_t e0, e1;
+    TFB_CUDA(cudaEventCreate(&e0));
+    TFB_CUDA(cudaEventCreate(&e1));
+    const int iters = 20000;
+    double best = 0;
+    for (int rep = 0; rep < 4; ++rep) {
+        TFB_CUDA(cudaEventRecord(e0, ctx->stream));
+        probe_tf32_kernel<<<ctx->sm_count, 128, smem, ctx->stream>>>(iters, ctx->dev_status);
+        TFB_CUDA(cudaEventRecord(e1, ctx->stream));
+        TFB_CUDA(cudaEventSynchronize(e1));
+        float ms = 0;
+        TFB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        const double flop = (double)ctx->sm_count * iters * 4 * (2.0 * 128 * 256 * 8);
+        const double t = flop / (ms * 1e-3) / 1e12;
+        if (rep > 0 && t > best) best = t;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *tflops = best;
+    return TFB_OK;
+}
 
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
     *declined = true;

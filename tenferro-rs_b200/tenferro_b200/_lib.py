@@ -91,6 +91,7 @@ PROTOTYPES = {
     "tfb_ctx_profile_end": (C.c_int, [_VP]),
     "tfb_probe_fp64_tflops": (C.c_int, [_VP, C.POINTER(C.c_double)]),
     "tfb_probe_hbm_gbs": (C.c_int, [_VP, C.POINTER(C.c_double)]),
+    "tfb_probe_tf32_tflops": (C.c_int, [_VP, C.POINTER(C.c_double)]),
     "tfb_event_record": (C.c_int, [_VP, _VPP]),
     "tfb_event_wait": (C.c_int, [_VP, _VP]),
     "tfb_event_synchronize": (C.c_int, [_VP]),

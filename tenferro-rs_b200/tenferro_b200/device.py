@@ -229,6 +229,11 @@ class Context:
         check(lib.tfb_probe_fp64_tflops(self.handle, C.byref(v)))
         return v.value
 
+    def probe_tf32_tflops(self) -> float:
+        v = C.c_double()
+        check(lib.tfb_probe_tf32_tflops(self.handle, C.byref(v)))
+        return v.value
+
     def probe_hbm_gbs(self) -> float:
         v = C.c_double()
         check(lib.tfb_probe_hbm_gbs(self.handle, C.byref(v)))

@@ -75,6 +75,14 @@ class _Block:
             pass
 
 
+class _Borrowed:
+    """Device memory owned by someone else (for example a torch tensor handed to NCCL):
+    `owner` is kept alive for as long as any view of the block exists."""
+
+    def __init__(self, ctx: Context, ptr: int, nbytes: int, owner):
+        self.ctx, self.ptr, self.nbytes, self.owner = ctx, ptr, nbytes, owner
+
+
 def make_view(ptr: int, dims, strides, offset: int, conj: bool, keep: list) -> _lib.TfbView:
     """Build a tfb_view; the ctypes arrays are appended to `keep` so they outlive the call."""
     n = len(dims)
@@ -152,6 +160,14 @@ class Tensor:
         array = np.asarray(array)
         flat = array.reshape(-1, order="F" if order == MemoryOrder.ColumnMajor else "C")
         return cls.from_slice(flat, array.shape, order, memory_space)
+
+    @classmethod
+    def from_device_pointer(cls, ptr: int, nbytes: int, dims, dtype, memory_space, owner=None,
+                            order=MemoryOrder.ColumnMajor, strides=None, offset=0) -> "Tensor":
+        """View device memory allocated elsewhere (it must live in `memory_space`)."""
+        block = _Borrowed(cls._ctx_of(memory_space), int(ptr), int(nbytes), owner)
+        strides = contiguous_strides(dims, order) if strides is None else strides
+        return cls(block, dims, strides, offset, dtype, memory_space)
 
     @classmethod
     def _meta(cls, dims, strides=None, offset=0, dtype=np.float64, order=MemoryOrder.ColumnMajor) -> "Tensor":
