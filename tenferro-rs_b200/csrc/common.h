@@ -168,6 +168,7 @@ tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_ker
 tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p);
 tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
+tfb_status contract_c32_3m(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 
 tfb_status grouped_gemm_launch(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, Scalar alpha,
                                Scalar beta);

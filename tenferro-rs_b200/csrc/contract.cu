@@ -294,7 +294,10 @@ tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_ker
     bool declined = false;
     if (want == CK_AUTO || want == CK_TCGEN05) {
         if (p.dtype == TFB_F32 || p.dtype == TFB_C32) {
-            TFB_TRY(contract_tcgen05(ctx, p, &declined));
+            if (p.dtype == TFB_C32)
+                TFB_TRY(contract_c32_3m(ctx, p, &declined));
+            else
+                TFB_TRY(contract_tcgen05(ctx, p, &declined));
             if (!declined) {
                 if (used) *used = "tcgen05_tf32x3";
                 return TFB_OK;

@@ -23,7 +23,7 @@
 // Operands may be K-major (contracted group has unit stride) or MN-major (free group has
 // unit stride); the instruction descriptor's major bits select the layout, so neither needs
 // a transpose pass.  Layouts TMA cannot describe (unit stride in neither group, strides that
-// are not multiples of 16 bytes, more than one non-fusable mode per group) are declined and
+// are not multiples of 16 bytes, more than two non-fusable modes per group) are declined and
 // run on the SIMT kernel.
 //
 // Semantics: PrimDescriptor::{Contract, BatchedGemm}, tenferro-prims/src/lib.rs:156-168, 227-239.
@@ -39,6 +39,17 @@ namespace {
 constexpr int kBM = 128, kBK = 32;  // tile rows, k per stage (32 f32 = one 128-byte swizzle row)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
+// How one operand's tile maps onto its rank-5 tensor map.  A group (M, N or K) may hold up to
+// two non-fusable modes (inner e1, outer e2); tiles either stay inside the inner mode (INNER:
+// a tile is a range of the inner index for one outer index, padded with TMA's zero fill) or,
+// when the inner extent divides the tile, pack several outer indices (PACK).
+struct TcGeom {
+    int mn_major;  // 0: K-major tile (K has unit stride), 1: MN-major tile (free group has unit stride)
+    int pack;      // free group tiling: 0 INNER, 1 PACK
+    int e1;        // extent of the free group's inner mode (of the whole group if it has one mode)
+    int tiles1;    // INNER: tiles per inner-mode slice
+};
+
 struct TcArgs {
     char* c;
     const int64_t* c_b;
@@ -46,9 +57,10 @@ struct TcArgs {
     const int64_t* c_n;
     int64_t M, N, K, B;
     float alpha, beta;
-    int a_mn_major, b_mn_major;  // 0: K-major tile, 1: MN-major tile
+    TcGeom a, b;
+    int k_e1, k_blocks1, num_kb;  // inner K extent, k-blocks per inner K slice, k-blocks in total
     int64_t tiles_m, tiles_n;
-    int group_m;                 // m-tiles per raster group (L2 reuse)
+    int group_m;                  // m-tiles per raster group (L2 reuse)
     int* status;
 };
 
@@ -83,11 +95,34 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* st
     atomicCAS(status, 0, code);
 }
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
+}
+
+// First row (linear index in the group), valid rows and tensor-map coordinates of free-group tile `t`.
+struct TileRows {
+    int64_t base;
+    int valid, f1, f2;
+};
+__device__ __forceinline__ TileRows tile_rows(const TcGeom& g, int64_t t, int rows_per_tile, int64_t total) {
+    TileRows r;
+    if (g.pack) {
+        r.base = t * rows_per_tile;
+        r.f1 = 0;
+        r.f2 = (int)(r.base / g.e1);
+        r.valid = (int)min((int64_t)rows_per_tile, total - r.base);
+    } else {
+        const int64_t f2 = t / g.tiles1;
+        r.f1 = (int)(t - f2 * g.tiles1) * rows_per_tile;
+        r.f2 = (int)f2;
+        r.base = f2 * g.e1 + r.f1;
+        r.valid = min(rows_per_tile, g.e1 - r.f1);
+    }
+    return r;
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
@@ -198,8 +233,8 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int64_t in_grp = tile - grp * group_sz;
     const int64_t tm = first_m + in_grp % rows_in_group;
     const int64_t tn = in_grp / rows_in_group;
-    const int m0 = (int)(tm * kBM), n0 = (int)(tn * BN);
-    const int num_kb = (int)((g.K + kBK - 1) / kBK);
+    const TileRows tr_m = tile_rows(g.a, tm, kBM, g.M), tr_n = tile_rows(g.b, tn, BN, g.N);
+    const int num_kb = g.num_kb;
     const int num_chunks = (num_kb + kChunk - 1) / kChunk;
 
     if (threadIdx.x == 0) {
@@ -233,35 +268,50 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
                 const uint32_t b_dst = a_dst + Cfg::A_BYTES;
                 mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
-                const int k0 = kb * kBK;
-                if (g.a_mn_major) {
-                    // [32 k][32 m] boxes, one per 32 rows of the tile
-                    for (int c = 0; c < kBM / 32; ++c)
-                        tma_load_3d(a_dst + c * 4096, &map_a, bar_full(s), m0 + 32 * c, k0, (int)bb);
+                const int k2 = kb / g.k_blocks1, k1 = (kb - k2 * g.k_blocks1) * kBK;
+                if (g.a.mn_major) {
+                    // [32 k][32 m] boxes, one per 32 rows of the tile; with packed tiling every
+                    // box finds its own (inner, outer) coordinates from its linear row
+                    for (int c = 0; c < kBM / 32; ++c) {
+                        int f1 = tr_m.f1 + 32 * c, f2 = tr_m.f2;
+                        if (g.a.pack) {
+                            const int64_t row = tr_m.base + 32 * c;
+                            f2 = (int)(row / g.a.e1);
+                            f1 = (int)(row - (int64_t)f2 * g.a.e1);
+                        }
+                        tma_load_5d(a_dst + c * 4096, &map_a, bar_full(s), f1, f2, k1, k2, (int)bb);
+                    }
                 } else {
-                    tma_load_3d(a_dst, &map_a, bar_full(s), k0, m0, (int)bb);
+                    tma_load_5d(a_dst, &map_a, bar_full(s), k1, k2, tr_m.f1, tr_m.f2, (int)bb);
                 }
-                if (g.b_mn_major) {
-                    for (int c = 0; c < BN / 32; ++c)
-                        tma_load_3d(b_dst + c * 4096, &map_b, bar_full(s), n0 + 32 * c, k0, (int)bb);
+                if (g.b.mn_major) {
+                    for (int c = 0; c < BN / 32; ++c) {
+                        int f1 = tr_n.f1 + 32 * c, f2 = tr_n.f2;
+                        if (g.b.pack) {
+                            const int64_t row = tr_n.base + 32 * c;
+                            f2 = (int)(row / g.b.e1);
+                            f1 = (int)(row - (int64_t)f2 * g.b.e1);
+                        }
+                        tma_load_5d(b_dst + c * 4096, &map_b, bar_full(s), f1, f2, k1, k2, (int)bb);
+                    }
                 } else {
                     // box rows are capped at 256 by the hardware; BN <= 256
-                    tma_load_3d(b_dst, &map_b, bar_full(s), k0, n0, (int)bb);
+                    tma_load_5d(b_dst, &map_b, bar_full(s), k1, k2, tr_n.f1, tr_n.f2, (int)bb);
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)g.a_mn_major << 15) |
-                                   ((uint32_t)g.b_mn_major << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)g.a.mn_major << 15) |
+                                   ((uint32_t)g.b.mn_major << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
             // K-major: rows of 128 bytes, 8-row atoms 1024 bytes apart; a k step moves 32 bytes
             // inside the row.  MN-major: [32 k][32 mn] blocks 4096 bytes apart (leading offset),
             // swizzle atoms of 4 k-rows 512 bytes apart (stride offset); a k step of 8 moves 1024 bytes.
-            const uint32_t a_lbo = g.a_mn_major ? 4096u : 16u, b_lbo = g.b_mn_major ? 4096u : 16u;
-            const uint32_t a_sbo = g.a_mn_major ? 512u : 1024u, b_sbo = g.b_mn_major ? 512u : 1024u;
-            const uint32_t a_lay = g.a_mn_major ? 1u : 2u, b_lay = g.b_mn_major ? 1u : 2u;
-            const uint32_t a_step = g.a_mn_major ? 1024u : 32u, b_step = g.b_mn_major ? 1024u : 32u;
+            const uint32_t a_lbo = g.a.mn_major ? 4096u : 16u, b_lbo = g.b.mn_major ? 4096u : 16u;
+            const uint32_t a_sbo = g.a.mn_major ? 512u : 1024u, b_sbo = g.b.mn_major ? 512u : 1024u;
+            const uint32_t a_lay = g.a.mn_major ? 1u : 2u, b_lay = g.b.mn_major ? 1u : 2u;
+            const uint32_t a_step = g.a.mn_major ? 1024u : 32u, b_step = g.b.mn_major ? 1024u : 32u;
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t use = kb / STAGES;
@@ -348,16 +398,15 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         while (next_promote < num_chunks) promote(next_promote++);
 
         const int row = lane_grp * 32 + lane;
-        const int64_t m = (int64_t)m0 + row;
-        if (m < g.M) {
+        if (row < tr_m.valid) {
             float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
-            const int64_t cm = g.c_m[m];
+            const int64_t cm = g.c_m[tr_m.base + row];
             const bool read_c = g.beta != 0.f;
 #pragma unroll
             for (int j = 0; j < CPW; ++j) {
-                const int64_t n = (int64_t)n0 + col0 + j;
-                if (n < g.N) {
-                    float* p = C + cm + g.c_n[n];
+                const int col = col0 + j;
+                if (col < tr_n.valid) {
+                    float* p = C + cm + g.c_n[tr_n.base + col];
                     float v = g.alpha * acc[j];
                     if (read_c) v += g.beta * *p;
                     *p = v;
@@ -390,51 +439,86 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// One operand as TMA sees it: a (rows x K) matrix per batch entry with one unit-stride side.
+// One operand as TMA sees it: a rank-5 tensor [major1, major2, minor1, minor2, batch] where the
+// "major" group is the one with the unit stride (K for a K-major tile, the free group for an
+// MN-major tile) and every group holds at most two modes.
 struct OperandMap {
     bool ok = false;
-    bool mn_major = false;
+    TcGeom geom{};
     CUtensorMap map;
 };
 
-// `free` = the M (or N) group, `k` = the contracted group, tns = tensor index (0: A, 1: B).
-OperandMap make_operand_map(const ContractProblem& p, const std::vector<Mode>& free, int tns, const void* base,
-                            int free_box_rows) {
+struct GroupDims {
+    int64_t e1 = 1, s1 = 0, e2 = 1, s2 = 0;  // inner / outer extent and stride (elements)
+    bool two = false;
+};
+bool group_dims(const std::vector<Mode>& g, int tns, GroupDims* out) {
+    if (g.size() > 2) return false;
+    if (g.size() >= 1) { out->e1 = g[0].extent; out->s1 = g[0].s[tns]; }
+    if (g.size() == 2) { out->e2 = g[1].extent; out->s2 = g[1].s[tns]; out->two = true; }
+    return true;
+}
+
+// `free` = the M (or N) group, tns = tensor index (0: A, 1: B), rows = tile rows (128 or BN).
+OperandMap make_operand_map(const ContractProblem& p, const std::vector<Mode>& free, int tns, const void* base, int rows) {
     OperandMap out;
     EncodeTiledFn enc = encode_fn();
-    if (!enc) return out;
-    if (free.size() > 1 || p.k.size() != 1 || p.batch.size() > 1) return out;
-    const int64_t rows = free.empty() ? 1 : free[0].extent, rs = free.empty() ? 0 : free[0].s[tns];
-    const int64_t K = p.k[0].extent, ks = p.k[0].s[tns];
-    const int64_t B = p.batch.empty() ? 1 : p.batch[0].extent, bs = p.batch.empty() ? 0 : p.batch[0].s[tns];
+    if (!enc || p.batch.size() > 1) return out;
+    GroupDims f, k;
+    if (!group_dims(free, tns, &f) || !group_dims(p.k, tns, &k)) return out;
     if ((uintptr_t)base % 16 != 0) return out;
-    cuuint64_t dims[3], strides[2];
-    cuuint32_t box[3], estr[3] = {1, 1, 1};
-    auto stride_ok = [](int64_t s) { return s > 0 && (s * 4) % 16 == 0; };
-    // A size-1 dimension has no meaningful stride; give it a legal one.
-    const int64_t batch_stride = (B > 1) ? bs : std::max<int64_t>(rows, 1) * std::max<int64_t>(K, 1);
-    if (ks == 1 && (rows == 1 || stride_ok(rs))) {
-        out.mn_major = false;
-        dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows; dims[2] = (cuuint64_t)B;
-        strides[0] = (cuuint64_t)((rows == 1 ? ((K + 3) / 4 * 4) : rs) * 4);
-        box[0] = kBK; box[1] = (cuuint32_t)free_box_rows; box[2] = 1;
-    } else if (rs == 1 && rows > 1 && (K == 1 || stride_ok(ks))) {
-        out.mn_major = true;
-        dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)B;
-        strides[0] = (cuuint64_t)((K == 1 ? ((rows + 3) / 4 * 4) : ks) * 4);
-        box[0] = 32; box[1] = kBK; box[2] = 1;
+    const int64_t B = p.batch.empty() ? 1 : p.batch[0].extent, bs = p.batch.empty() ? 0 : p.batch[0].s[tns];
+    auto aligned = [](int64_t s) { return s > 0 && s % 4 == 0; };  // 16-byte multiples, positive
+    TcGeom& g = out.geom;
+    cuuint64_t dims[5], strides[4];
+    cuuint32_t box[5] = {1, 1, 1, 1, 1}, estr[5] = {1, 1, 1, 1, 1};
+    // Strides of size-1 dimensions are never used for addressing; any 16-byte multiple will do.
+    auto stride_or_dummy = [&](int64_t extent, int64_t s) -> int64_t { return extent > 1 ? s : 4; };
+    g.e1 = (int)f.e1;
+    if (k.s1 == 1 && k.e1 >= 1) {
+        // K-major: unit stride on the inner K mode.
+        g.mn_major = 0;
+        if ((k.two && !aligned(k.s2)) || (f.e1 > 1 && !aligned(f.s1)) || (f.two && f.e2 > 1 && !aligned(f.s2))) return out;
+        dims[0] = k.e1; dims[1] = k.e2; dims[2] = f.e1; dims[3] = f.e2; dims[4] = B;
+        strides[0] = stride_or_dummy(k.e2, k.s2) * 4;
+        strides[1] = stride_or_dummy(f.e1, f.s1) * 4;
+        strides[2] = stride_or_dummy(f.e2, f.s2) * 4;
+        strides[3] = stride_or_dummy(B, bs) * 4;
+        box[0] = kBK;
+        if (f.two && f.e1 < rows && rows % f.e1 == 0) {
+            g.pack = 1; g.tiles1 = 1;
+            box[2] = (cuuint32_t)f.e1; box[3] = (cuuint32_t)(rows / f.e1);
+        } else {
+            g.pack = 0; g.tiles1 = (int)((f.e1 + rows - 1) / rows);
+            box[2] = (cuuint32_t)rows;
+        }
+    } else if (f.s1 == 1 && f.e1 > 1) {
+        // MN-major: unit stride on the inner free mode; boxes are [32 k][32 mn].
+        g.mn_major = 1;
+        if ((f.two && f.e2 > 1 && !aligned(f.s2)) || (k.e1 > 1 && !aligned(k.s1)) || (k.two && k.e2 > 1 && !aligned(k.s2))) return out;
+        dims[0] = f.e1; dims[1] = f.e2; dims[2] = k.e1; dims[3] = k.e2; dims[4] = B;
+        strides[0] = stride_or_dummy(f.e2, f.s2) * 4;
+        strides[1] = stride_or_dummy(k.e1, k.s1) * 4;
+        strides[2] = stride_or_dummy(k.e2, k.s2) * 4;
+        strides[3] = stride_or_dummy(B, bs) * 4;
+        box[0] = 32; box[2] = kBK;
+        if (f.two && f.e1 % 32 == 0) {
+            g.pack = 1; g.tiles1 = 1;  // tiles follow the linear row index; each 32-row box is placed on its own
+        } else {
+            g.pack = 0; g.tiles1 = (int)((f.e1 + rows - 1) / rows);
+        }
     } else {
         return out;
     }
-    if (B > 1 && !stride_ok(bs)) return out;
-    strides[1] = (cuuint64_t)(((B > 1) ? bs : ((batch_stride + 3) / 4 * 4)) * 4);
-    if (strides[0] % 16 != 0 || strides[1] % 16 != 0) return out;
-    if (strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return out;
-    CUresult r = enc(&out.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+    if (B > 1 && !aligned(bs)) return out;
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] % 16 != 0 || strides[i] >= (1ull << 40)) return out;
+    for (int i = 0; i < 5; ++i)
+        if (dims[i] == 0 || dims[i] > 0xffffffffull) return out;
+    CUresult r = enc(&out.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     out.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     g.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     out.ok = (r == CUDA_SUCCESS);
     return out;
 }
@@ -452,8 +536,14 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
             configured[ctx->device] = true;
         }
     }
-    g.tiles_m = (g.M + kBM - 1) / kBM;
-    g.tiles_n = (g.N + BN - 1) / BN;
+    g.a = a.geom;
+    g.b = b.geom;
+    auto tiles = [](const TcGeom& o, int64_t total, int rows) -> int64_t {
+        if (o.pack) return (total + rows - 1) / rows;
+        return (total / o.e1) * o.tiles1;  // outer extent x tiles per inner slice
+    };
+    g.tiles_m = tiles(g.a, g.M, kBM);
+    g.tiles_n = tiles(g.b, g.N, BN);
     g.group_m = 16;
     const int64_t grid = g.tiles_m * g.tiles_n * g.B;
     if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
@@ -556,8 +646,10 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     g.M = M; g.N = N; g.K = K; g.B = p.B();
     g.alpha = (float)p.alpha.re;
     g.beta = (float)p.beta.re;
-    g.a_mn_major = a.mn_major;
-    g.b_mn_major = b.mn_major;
+    // Both operands walk K in the same blocks: 32 at a time inside the inner K mode.
+    g.k_e1 = (int)p.k[0].extent;
+    g.k_blocks1 = (g.k_e1 + kBK - 1) / kBK;
+    g.num_kb = (int)((K / g.k_e1) * g.k_blocks1);
     g.status = ctx->dev_status;
     *declined = false;
     return bn == 256 ? launch_tc<256>(ctx, a, b, g) : launch_tc<128>(ctx, a, b, g);

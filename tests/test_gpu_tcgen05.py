@@ -86,3 +86,59 @@ def test_einsum_ijkl_klmn_uses_tensor_cores(tb, oracle):
     tb.CudaBackend.execute(plan, 1.0, [tb.Tensor.from_numpy(a), tb.Tensor.from_numpy(b)], 0.0, out)
     assert plan.kernel_name == "tcgen05_tf32x3"
     assert oracle.rel_frobenius(out.to_numpy(), oracle.np_einsum("ijkl,klmn->ijmn", [a, b])) <= 1e-5
+
+
+@pytest.mark.parametrize("case", [
+    # (labels_a, shape_a, labels_b, shape_b, labels_c): groups with two non-fusable modes each way
+    ("free pair, MN-major, packed", [0, 1, 2], (64, 6, 40), [2, 3], (40, 72), [0, 1, 3], "sub_i"),
+    ("free pair, K-major, inner extent 96 padded to the tile", [2, 0, 1], (64, 96, 5), [2, 3], (64, 160), [0, 1, 3], None),
+    ("free pair, K-major, packed small inner extent", [2, 0, 1], (48, 32, 9), [2, 3], (48, 96), [0, 1, 3], None),
+    ("contracted pair not fusable in B", [0, 1, 2], (96, 96, 40), [3, 2, 1, 4], (24, 40, 96, 3), [0, 3, 4], None),
+    ("dim-96 network step", [0, 1, 2], (96, 96, 96), [3, 2, 1, 4], (96, 96, 96, 8), [0, 3, 4], None),
+])
+def test_tf32x3_two_modes_per_group(tb, oracle, case):
+    name, la, sa, lb, sb, lc, special = case
+    rng = np.random.default_rng(sum(sa) + sum(sb))
+    a, b = random_array(rng, sa, np.float32), random_array(rng, sb, np.float32)
+    ext = dict(zip(la, sa))
+    ext.update(dict(zip(lb, sb)))
+    sc = tuple(ext[l] for l in lc)
+    ta, tbt = tb.Tensor.from_numpy(a), tb.Tensor.from_numpy(b)
+    if special == "sub_i":
+        # a strided sub-view: the first half of mode 0 (what sharding a free index produces)
+        half = sa[0] // 2
+        ta = tb.Tensor(ta._block, (half,) + tuple(sa[1:]), ta.strides(), 0, np.float32, ta.logical_memory_space())
+        a = a[:half]
+        sc = (half,) + sc[1:]
+    plan = tb.CudaBackend.plan(tb.PrimDescriptor.Contract(la, lb, lc), [a.shape, b.shape, sc], np.float32)
+    out = tb.Tensor.zeros(sc, dtype=np.float32)
+    tb.CudaBackend.execute(plan, 1.0, [ta, tbt], 0.0, out)
+    assert plan.kernel_name == "tcgen05_tf32x3", (name, plan.kernel_name)
+    want = oracle.np_contract(la, a, lb, b, lc)
+    assert oracle.rel_frobenius(out.to_numpy(), want) <= 1e-5, name
+
+
+@pytest.mark.parametrize("shape", [(64, 96, 40), (130, 70, 33), (256, 256, 512), (96, 9216, 96)])
+def test_complex64_three_products_on_tensor_cores(tb, oracle, shape):
+    """Complex32 contractions: planes gathered from any layout (conj folded in), three real
+    3xTF32 products, complex alpha/beta on the way out."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    for trial, layout in enumerate(("col", "row", "random")):
+        a = Strided(random_array(rng, (m, k), np.complex64), rng, layout, conj=bool(trial % 2))
+        b = Strided(random_array(rng, (k, n), np.complex64), rng, layout, conj=bool(trial == 2))
+        c = Strided(random_array(rng, (m, n), np.complex64), rng, layout if layout != "random" else "col")
+        alpha, beta = [(1.0, 0.0), (0.5 - 0.25j, 1.5j), (-1.0, 1.0)][trial]
+        plan = tb.CudaBackend.plan(tb.PrimDescriptor.Contract([0, 1], [1, 2], [0, 2]), [(m, k), (k, n), (m, n)], np.complex64)
+        out = c.to_device(tb)
+        tb.CudaBackend.execute(plan, alpha, [a.to_device(tb), b.to_device(tb)], beta, out)
+        assert plan.kernel_name == "tcgen05_tf32x3", (layout, plan.kernel_name)
+        want = oracle.np_contract([0, 1], a.logical, [1, 2], b.logical, [0, 2], alpha, beta, c.logical)
+        err = oracle.rel_frobenius(out.to_numpy(), want)
+        assert err <= 1e-5, (err, layout, shape)
+
+
+def test_network_einsum_complex64_dim32(tb, oracle):
+    ops = [oracle.normal(4000 + i, (32, 32, 32), np.complex64) for i in range(4)]
+    got = tb.einsum("ijk,jlm,kmn,lnp->ip", [tb.Tensor.from_numpy(o) for o in ops]).to_numpy()
+    assert oracle.rel_frobenius(got, oracle.np_einsum("ijk,jlm,kmn,lnp->ip", ops)) <= 1e-5
