@@ -341,6 +341,8 @@ def wl_chain(env: Env):
 
 def wl_dense(env: Env):
     """'ijkl,klmn->ijmn', f32, N(0,1).  Strong scaling: the ranks split one contraction."""
+    from tenferro_b200 import sharding
+
     args, tb, ctx, torch = env.args, env.tb, env.ctx, env.torch
     e = lambda x: max(4, int(round(x * args.scale / 4)) * 4)
     i = j = m = n = e(128)
@@ -360,11 +362,11 @@ def wl_dense(env: Env):
     if args.shard == "i" or W == 1:
         if i % W:
             raise SystemExit("i must divide by the number of GPUs")
-        iw = i // W
         c_t = torch.zeros((n, m, j, i), device=dev, dtype=torch.float32)
         Cfull = wrap(c_t, [i, j, m, n])
-        As = tb.Tensor(A._block, [iw, j, k, l], A.strides(), r * iw, np.float32, env.space)
-        Cs = tb.Tensor(Cfull._block, [iw, j, m, n], Cfull.strides(), r * iw, np.float32, env.space)
+        view = lambda T, axis: tb.Tensor(T._block, *sharding.shard_view(T.dims(), T.strides(), 0, axis, W, r),
+                                         np.float32, env.space)
+        As, Cs = view(A, 0), view(Cfull, 0)
         tree = tb.ContractionTree.optimize(tb.Subscripts.parse(notation), [As.dims(), B.dims()])
         call = tb.PreparedEinsum(tree, [As, B], Cs)
         step = call.run
@@ -373,12 +375,12 @@ def wl_dense(env: Env):
     else:
         if l % W:
             raise SystemExit("l must divide by the number of GPUs")
-        lw = l // W
         part_t = torch.zeros((n, m, j, i), device=dev, dtype=torch.float32)
         out_t = torch.zeros((n * m * j * i) // W, device=dev, dtype=torch.float32)
         P = wrap(part_t, [i, j, m, n])
-        As = tb.Tensor(A._block, [i, j, k, lw], A.strides(), r * lw * A.strides()[3], np.float32, env.space)
-        Bs = tb.Tensor(B._block, [k, lw, m, n], B.strides(), r * lw * B.strides()[1], np.float32, env.space)
+        view = lambda T, axis: tb.Tensor(T._block, *sharding.shard_view(T.dims(), T.strides(), 0, axis, W, r),
+                                         np.float32, env.space)
+        As, Bs = view(A, 3), view(B, 1)
         tree = tb.ContractionTree.optimize(tb.Subscripts.parse(notation), [As.dims(), Bs.dims()])
         call = tb.PreparedEinsum(tree, [As, Bs], P)
 
@@ -413,13 +415,13 @@ def wl_dense(env: Env):
 def wl_grouped(env: Env):
     """4096 ragged 'ij,jk->ik' products, f32, dims from {16,32,64,128}, U(-1,1); table sharded."""
     from oracle import oracle
+    from tenferro_b200 import sharding
 
     args, tb, ctx, torch = env.args, env.tb, env.ctx, env.torch
     table = oracle.grouped_table(3000, args.problems)
     bytes_p = 4 * (table[:, 0] * table[:, 1] + table[:, 1] * table[:, 2] + table[:, 0] * table[:, 2])
     # contiguous ranges of the table with equal byte counts
-    cum = np.concatenate([[0], np.cumsum(bytes_p)])
-    cuts = [int(np.searchsorted(cum, cum[-1] * q / env.world)) for q in range(env.world + 1)]
+    cuts = sharding.split_table_by_bytes(bytes_p, env.world)
     lo, hi = cuts[env.rank], cuts[env.rank + 1]
     mine = table[lo:hi]
     dev = torch.device("cuda", env.local_rank)

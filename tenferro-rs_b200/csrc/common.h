@@ -70,6 +70,12 @@ struct tfb_ctx {
     size_t smem_optin = 0;
     // One-word device status used by kernels with bounded waits (0 = fine).
     int* dev_status = nullptr;
+    // Scratch of the in-kernel stream-K reduction: one accumulator slot and one flag per CTA.
+    void* sk_partial = nullptr;
+    size_t sk_partial_bytes = 0;
+    unsigned* sk_flags = nullptr;
+    size_t sk_flags_n = 0;
+    unsigned sk_epoch = 0;
     // Optional per-launch timing (tfb_ctx_profile_*): event pairs around named launches.
     bool profiling = false;
     struct ProfRec {

@@ -186,6 +186,8 @@ tfb_status tfb_ctx_destroy(tfb_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->sk_partial) cudaFree(ctx->sk_partial);
+    if (ctx->sk_flags) cudaFree(ctx->sk_flags);
     delete ctx;
     return TFB_OK;
 }

@@ -35,6 +35,8 @@ struct ContractArgs {
     // Work decomposition: tiles x k-iterations, cut into equal contiguous ranges ("stream-K").
     int64_t tiles_m, tiles_n, n_tiles, k_iters, total_iters, iters_per_cta;
     int debug;
+    unsigned* sk_flags;  // per-CTA flags of the in-kernel stream-K reduction (TMA-fed DMMA kernel)
+    unsigned sk_epoch;   // a flag is raised when it equals this launch's epoch
     char* partial;  // 2 slots of one block tile per CTA, used only by ranges that cut a tile
 };
 

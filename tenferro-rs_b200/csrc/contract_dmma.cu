@@ -467,6 +467,17 @@ static tfb_status run_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractArgs a
     return TFB_OK;
 }
 
+}  // namespace tfb
+
+#include "contract_dmma_tma.cuh"
+
+namespace tfb {
+
+using RealTma = DmmaTmaCfg<false, 128, 128, 16, 4, 4, 6>;
+using CplxTma = DmmaTmaCfg<true, 64, 64, 16, 4, 4, 6>;
+using RealTmaSmall = DmmaTmaCfg<false, 64, 64, 16, 2, 2, 8>;
+using CplxTmaSmall = DmmaTmaCfg<true, 32, 32, 16, 2, 2, 8>;
+using RealTmaTiny = DmmaTmaCfg<false, 32, 32, 16, 2, 2, 8>;
 using RealBig = DmmaCfg<false, 128, 128, 16, 4, 4, 3>;
 using RealBig8 = DmmaCfg<false, 128, 128, 16, 2, 4, 3>;
 using RealSmall = DmmaCfg<false, 64, 64, 16, 2, 2, 4>;
@@ -485,16 +496,35 @@ tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined)
     fill_args(p, *t, &a);
     a.debug = env_int("TFB_DEBUG_SKIP", 0);
     const int shape = env_int("TFB_DMMA_TILE", 0);  // 0 auto, 1 small, 2 big
+    const bool use_tma = !env_int("TFB_NO_DMMA_TMA", 0);
     if (p.dtype == TFB_F64) {
         bool small = (a.M <= 64 || a.N <= 64 || a.M * a.N * a.B < (int64_t)128 * 128 * ctx->sm_count / 2);
         if (shape == 1) small = true;
         if (shape == 2) small = false;
         if (shape == 3) return run_cfg<RealBig8>(ctx, p, a);
+        if (use_tma) {
+            bool d = true;
+            if (a.M * a.N * a.B <= 64 * 64)
+                TFB_TRY(run_tma_cfg<RealTmaTiny>(ctx, p, a, &d));  // few outputs, long K: many small ranges
+            else if (small)
+                TFB_TRY(run_tma_cfg<RealTmaSmall>(ctx, p, a, &d));
+            else
+                TFB_TRY(run_tma_cfg<RealTma>(ctx, p, a, &d));
+            if (!d) return TFB_OK;
+        }
         return small ? run_cfg<RealSmall>(ctx, p, a) : run_cfg<RealBig>(ctx, p, a);
     }
     bool small = (a.M <= 32 || a.N <= 32);
     if (shape == 1) small = true;
     if (shape == 2) small = false;
+    if (use_tma) {
+        bool d = true;
+        if (small)
+            TFB_TRY(run_tma_cfg<CplxTmaSmall>(ctx, p, a, &d));
+        else
+            TFB_TRY(run_tma_cfg<CplxTma>(ctx, p, a, &d));
+        if (!d) return TFB_OK;
+    }
     return small ? run_cfg<CplxSmall>(ctx, p, a) : run_cfg<CplxMain>(ctx, p, a);
 }
 

@@ -311,12 +311,30 @@ __global__ void __launch_bounds__(256) reduce_kernel(LoopNest kept, LoopNest red
         for (int64_t ko = (int64_t)blockIdx.x * 8 + warp; ko < kept.total; ko += warps_total) {
             int64_t koff[2];
             decompose<2>(kept, 0, ko, koff);
-            T acc = Red<T, OP>::init();
-            for (int64_t r = r0 + lane; r < r1; r += 32) {
+            // Walk the reduced range in runs along its innermost mode (no division per
+            // element); eight independent partial results per lane keep loads in flight.
+            T part[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) part[u] = Red<T, OP>::init();
+            const int64_t e0 = red.extent[0], s0 = red.stride[0][0];
+            int64_t r = r0;
+            while (r < r1) {
+                int64_t q, i0;
+                divmod(r, e0, q, i0);
                 int64_t roff[1];
-                decompose<1>(red, 0, r, roff);
-                acc = Red<T, OP>::comb(acc, in[koff[0] + roff[0]]);
+                decompose<1>(red, 1, q, roff);
+                const int64_t run = min(e0 - i0, r1 - r);
+                const T* p = in + koff[0] + roff[0] + i0 * s0;
+                int64_t i = lane;
+                for (; i + 224 < run; i += 256) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) part[u] = Red<T, OP>::comb(part[u], p[(i + 32 * u) * s0]);
+                }
+                for (; i < run; i += 32) part[0] = Red<T, OP>::comb(part[0], p[i * s0]);
+                r += run;
             }
+            T acc = Red<T, OP>::comb(Red<T, OP>::comb(Red<T, OP>::comb(part[0], part[1]), Red<T, OP>::comb(part[2], part[3])),
+                                     Red<T, OP>::comb(Red<T, OP>::comb(part[4], part[5]), Red<T, OP>::comb(part[6], part[7])));
 #pragma unroll
             for (int s = 16; s > 0; s >>= 1) acc = Red<T, OP>::comb(acc, Ops<T>::shfl_down(acc, s));
             if (lane == 0) {
