@@ -78,10 +78,26 @@ def chain_flops(chi: int, d: int, sites: int) -> float:
     return sites * 2 * 8.0 * chi * chi * (d * chi)
 
 
-def site_tensor(seed: int, chi: int, d: int) -> np.ndarray:
-    from oracle import oracle
+def seeded_normal(seed: int, shape, dtype, scale: float = 1.0) -> np.ndarray:
+    """Column-major N(0, scale^2) tensor (real and imaginary parts alike), seed -> default_rng."""
+    rng = np.random.default_rng(seed)
+    dtype = np.dtype(dtype)
+    if dtype.kind == "c":
+        real = np.float32 if dtype == np.complex64 else np.float64
+        out = np.empty(shape, dtype=dtype, order="F")
+        out.real = rng.standard_normal(shape).astype(real) * scale
+        out.imag = rng.standard_normal(shape).astype(real) * scale
+        return out
+    return np.asfortranarray((rng.standard_normal(shape) * scale).astype(dtype))
 
-    return oracle.normal(seed, (chi, d, chi), np.complex128, scale=(1.0 / chi) ** 0.5)
+
+def grouped_table(seed: int, n_problems: int) -> np.ndarray:
+    """(n, 3) table of (i, j, k) drawn uniformly from {16, 32, 64, 128}."""
+    return np.random.default_rng(seed).choice(np.array([16, 32, 64, 128]), size=(n_problems, 3))
+
+
+def site_tensor(seed: int, chi: int, d: int) -> np.ndarray:
+    return seeded_normal(seed, (chi, d, chi), np.complex128, scale=(1.0 / chi) ** 0.5)
 
 
 # ------------------------------------------------------------------------------------------
@@ -414,11 +430,10 @@ def wl_dense(env: Env):
 
 def wl_grouped(env: Env):
     """4096 ragged 'ij,jk->ik' products, f32, dims from {16,32,64,128}, U(-1,1); table sharded."""
-    from oracle import oracle
     from tenferro_b200 import sharding
 
     args, tb, ctx, torch = env.args, env.tb, env.ctx, env.torch
-    table = oracle.grouped_table(3000, args.problems)
+    table = grouped_table(3000, args.problems)
     bytes_p = 4 * (table[:, 0] * table[:, 1] + table[:, 1] * table[:, 2] + table[:, 0] * table[:, 2])
     # contiguous ranges of the table with equal byte counts
     cuts = sharding.split_table_by_bytes(bytes_p, env.world)
@@ -442,8 +457,10 @@ def wl_grouped(env: Env):
     flops_all = float((2.0 * table[:, 0] * table[:, 1] * table[:, 2]).sum())
     bytes_all = float(bytes_p.sum())
 
-    def step():
-        tb.grouped_gemm(probs, np.float32, 1.0, 0.0, ctx)
+    from tenferro_b200.prims import PreparedGroupedGemm
+
+    call = PreparedGroupedGemm(probs, np.float32, 1.0, 0.0, ctx)
+    step = call.run
 
     def read_result():
         ctx.synchronize()
@@ -453,7 +470,8 @@ def wl_grouped(env: Env):
     return {
         "metric": "einsum GFLOP/s (grouped 'bij,bjk->bik', f32, ragged)", "unit": "GFLOP/s", "dtype": "f32",
         "scaling": "strong", "step": step, "work": flops_all, "read_result": read_result, "e2e_step": None, "h2d": 0,
-        "d2h": 0, "kernel": "grouped_simt", "kernel_label": "grouped_simt_kernel (persistent, atomic tile ticket)",
+        "d2h": 0, "kernel": "grouped_tf32x3", "kernels_any": ["grouped_tf32x3", "grouped_simt"],
+        "kernel_label": "grouped_tf32x3_kernel (persistent, atomic ticket, mma.sync 3xTF32)",
         "per_launch": float(bytes_p[lo:hi].sum()), "bound": "hbm",
         "peak": (lambda: hbm) if hbm else ctx.probe_hbm_gbs,
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if hbm else "library copy probe (MEASURED_PEAKS.json absent)",
@@ -467,12 +485,10 @@ def wl_grouped(env: Env):
 
 
 def wl_network4(env: Env):
-    from oracle import oracle
-
     args, tb, ctx = env.args, env.tb, env.ctx
     dim = max(8, int(round(96 * args.scale)))
     notation = "ijk,jlm,kmn,lnp->ip"
-    arrays = [oracle.normal(4000 + t, (dim,) * 3, np.complex64) for t in range(4)]
+    arrays = [seeded_normal(4000 + t, (dim,) * 3, np.complex64) for t in range(4)]
     ops = [tb.Tensor.from_numpy(a, memory_space=env.space) for a in arrays]
     out = tb.Tensor.empty([dim, dim], np.complex64, env.space)
     tree = tb.ContractionTree.optimize(tb.Subscripts.parse(notation), [a.shape for a in arrays])
@@ -497,11 +513,9 @@ def wl_network4(env: Env):
 
 
 def wl_abc_bcd(env: Env):
-    from oracle import oracle
-
     args, tb, ctx = env.args, env.tb, env.ctx
     notation = "abc,bcd->ad"
-    a, b = oracle.normal(1000, (64, 64, 64), np.float64), oracle.normal(1001, (64, 64, 64), np.float64)
+    a, b = seeded_normal(1000, (64, 64, 64), np.float64), seeded_normal(1001, (64, 64, 64), np.float64)
     A, B = tb.Tensor.from_numpy(a, memory_space=env.space), tb.Tensor.from_numpy(b, memory_space=env.space)
     out = tb.Tensor.empty([64, 64], np.float64, env.space)
     tree = tb.ContractionTree.optimize(tb.Subscripts.parse(notation), [a.shape, b.shape])

@@ -176,6 +176,8 @@ tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined)
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 tfb_status contract_c32_3m(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 
+tfb_status grouped_tf32_fast(tfb_ctx* ctx, size_t n, const tfb_gemm_problem* problems, Scalar alpha, Scalar beta,
+                             bool* declined);
 tfb_status grouped_gemm_launch(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, Scalar alpha,
                                Scalar beta);
 

@@ -151,6 +151,11 @@ tfb_status grouped_simt(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_proble
 tfb_status grouped_gemm_launch(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, Scalar alpha,
                                Scalar beta) {
     DeviceGuard g(ctx->device);
+    if (dtype == TFB_F32) {
+        bool declined = true;
+        TFB_TRY(grouped_tf32_fast(ctx, n, problems, alpha, beta, &declined));
+        if (!declined) return TFB_OK;
+    }
     return grouped_simt(ctx, dtype, n, problems, alpha, beta);
 }
 

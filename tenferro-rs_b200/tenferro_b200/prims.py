@@ -196,6 +196,23 @@ class CudaBackend:
         return bool(lib.tfb_has_extension(code, int(ext)))
 
 
+class PreparedGroupedGemm:
+    """A problem table marshalled once, for loops that run the same ragged batch repeatedly."""
+
+    def __init__(self, problems, dtype, alpha=1.0, beta=0.0, ctx: Optional[Context] = None):
+        self.ctx = ctx or Context.get(0)
+        problems = list(problems)
+        self.n = len(problems)
+        self.arr = (_lib.TfbGemmProblem * max(self.n, 1))()
+        for i, p in enumerate(problems):
+            self.arr[i] = _lib.TfbGemmProblem(*p)
+        self.code = dtype_code(dtype)
+        self.alpha, self.beta = scalar_arg(alpha, dtype), scalar_arg(beta, dtype)
+
+    def run(self) -> None:
+        check(lib.tfb_grouped_gemm(self.ctx.handle, self.code, self.n, self.arr, self.alpha, self.beta))
+
+
 def grouped_gemm(problems, dtype, alpha=1.0, beta=0.0, ctx: Optional[Context] = None) -> None:
     """Ragged batch of C_p = alpha * A_p @ B_p + beta * C_p in one persistent launch.
     `problems`: iterable of (m, n, k, a_ptr, a_rs, a_cs, b_ptr, b_rs, b_cs, c_ptr, c_rs, c_cs)."""
