@@ -346,6 +346,9 @@ def wl_chain(env: Env):
         "peak_source": "measured on this GPU by the library's register-resident DMMA probe "
                        "(MEASURED_PEAKS.json holds no FP64 figure)",
         "extra_kernels": ["contract_dmma_fixup"],
+        # dram__bytes_read + dram__bytes_write per launch from the ncu capture summarised in
+        # profiles/contract_dmma_c128_mps_chain.md (12.6 and 16.8 MB on the two captured launches)
+        "traffic": 14.74e6 if (chi, d) == (512, 2) else None,
         "config": {"workload": f"MPS transfer-matrix chain: {sites} sites, chi={chi}, d={d}, complex128, '{CHAIN}' "
                                f"per site via the contraction tree",
                    "parallelism": f"{env.world} independent replica(s)",
@@ -476,6 +479,8 @@ def wl_grouped(env: Env):
         "peak": (lambda: hbm) if hbm else ctx.probe_hbm_gbs,
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if hbm else "library copy probe (MEASURED_PEAKS.json absent)",
         "extra_kernels": [], "keep": (a_t, b_t, c_t),
+        # profiles/grouped_tf32x3_ragged_4096.md: 121.7 MB read + 34.6 MB written
+        "traffic": 156.3e6 if (args.problems == 4096 and env.world == 1) else None,
         "config": {"workload": f"{args.problems} problems 'ij,jk->ik', dims drawn from {{16,32,64,128}} (seed 3000), "
                                f"U(-1,1), f32", "parallelism": f"problem table split {env.world} ways by bytes",
                    "l2": f"inputs larger than L2: {bytes_all / 2**20:.0f} MiB touched per step",
@@ -581,6 +586,8 @@ def wl_permute(env: Env):
         "per_launch": bytes_step, "bound": "hbm", "peak": (lambda: hbm) if hbm else ctx.probe_hbm_gbs,
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if hbm else "library copy probe (MEASURED_PEAKS.json absent)",
         "extra_kernels": [], "keep": (src_t, dst_t),
+        # profiles/permute_tiled_vec_transpose2d_f32.md: 1.074 GB read + 1.031 GB written
+        "traffic": 2.105e9 if (args.case == "transpose2d" and args.scale == 1.0) else None,
         "config": {"workload": f"permute {list(shape)} {np.dtype(dtype).name} by {list(perm)}",
                    "parallelism": f"{env.world} replica(s)",
                    "l2": "inputs larger than L2" if n * itemsize > 200e6 else "fits L2 (small member of the set)",
@@ -629,6 +636,8 @@ def wl_reduce(env: Env):
         "peak": (lambda: hbm) if hbm else ctx.probe_hbm_gbs,
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if hbm else "library copy probe (MEASURED_PEAKS.json absent)",
         "extra_kernels": ["reduce_finish"], "keep": (src_t, dst_t),
+        # profiles/reduce_sum_axis0_f32.md: 1.076 GB read + 19.4 MB written
+        "traffic": 1.095e9 if args.case == "sum_axis0" else None,
         "config": {"workload": f"reduce {list(shape)} {np.dtype(dtype).name} keeping modes {kept}, op {op}",
                    "parallelism": f"{env.world} replica(s)", "l2": "inputs larger than L2", "bytes_total": bytes_step},
         "cpu": None,
@@ -727,7 +736,7 @@ def main():
     achieved = wl["per_launch"] / (ms_main / n_main * 1e-3) / scale if n_main else None
     roofline = {
         "bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": "TFLOP/s" if wl["bound"] == "tensor" else "GB/s",
-        "frac": (achieved / peak) if (achieved and peak) else None, "traffic": None,
+        "frac": (achieved / peak) if (achieved and peak) else None, "traffic": wl.get("traffic"),
         "kernel": wl["kernel_label"], "peak_source": wl["peak_source"], "launches": n_main,
         "avg_launch_us": ms_main / max(n_main, 1) * 1e3,
         "other_kernels": {k: {"launches": v[0], "avg_us": v[1] / max(v[0], 1) * 1e3} for k, v in extras.items()},

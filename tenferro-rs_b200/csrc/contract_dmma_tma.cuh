@@ -196,8 +196,8 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int64_t kit = kb; kit < ke; ++kit, ++n) {
             const int s = n % STAGES;
             if (is_producer) produce_until((int64_t)n + kLead + 1);
+            if (lane == 0) mbar_wait(bar_full(s), (n / STAGES) & 1, status, 0x302);
             __syncwarp();
-            mbar_wait(bar_full(s), (n / STAGES) & 1, status, 0x302);
             const char* sa = smem + (size_t)s * Cfg::STAGE_BYTES;
             const char* sb = sa + Cfg::A_BYTES;
             if (a_mn) {

@@ -61,6 +61,7 @@ struct TcArgs {
     int k_e1, k_blocks1, num_kb;  // inner K extent, k-blocks per inner K slice, k-blocks in total
     int64_t tiles_m, tiles_n;
     int group_m;                  // m-tiles per raster group (L2 reuse)
+    int elect;                    // 1: one lane per warp polls/arrives on mbarriers
     int* status;
 };
 
@@ -164,12 +165,12 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full(s), 1);
-            mbar_init(bar_split(s), kSplitThreads);
+            mbar_init(bar_split(s), g.elect ? kSplitThreads / 32 : kSplitThreads);
             mbar_init(bar_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_chunk(b), 1);
-            mbar_init(bar_promoted(b), kSplitThreads);
+            mbar_init(bar_promoted(b), g.elect ? kSplitThreads / 32 : kSplitThreads);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -282,7 +283,9 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         int next_promote = 0;
         auto promote = [&](int chunk) {
             const int buf = chunk & 1;
-            mbar_wait(bar_chunk(buf), (uint32_t)(chunk >> 1) & 1, g.status, 0x104);
+            // one lane polls, the warp follows: mbarrier operations of 32 lanes on one word serialise
+            if (lane == 0 || !g.elect) mbar_wait(bar_chunk(buf), (uint32_t)(chunk >> 1) & 1, g.status, 0x104);
+            __syncwarp();
             tc_fence_after();
 #pragma unroll
             for (int c0 = 0; c0 < CPW; c0 += 32) {
@@ -293,12 +296,14 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
             }
             tc_fence_before();
-            mbar_arrive(bar_promoted(buf));
+            __syncwarp();
+            if (lane == 0 || !g.elect) mbar_arrive(bar_promoted(buf));
         };
         for (int kb = 0; kb < num_kb; ++kb) {
             const int s = kb % STAGES;
             const uint32_t use = kb / STAGES;
-            mbar_wait(bar_full(s), use & 1, g.status, 0x103);
+            if (lane == 0 || !g.elect) mbar_wait(bar_full(s), use & 1, g.status, 0x103);
+            __syncwarp();
             char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
             char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
             constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
@@ -312,7 +317,8 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
             }
             fence_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
-            mbar_arrive(bar_split(s));
+            __syncwarp();
+            if (lane == 0 || !g.elect) mbar_arrive(bar_split(s));
             // A chunk whose last k-block lies STAGES behind has certainly retired: the stage
             // just split could only be loaded after that k-block's MMAs freed it.
             while (next_promote < num_chunks &&
@@ -468,7 +474,8 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     };
     g.tiles_m = tiles(g.a, g.M, kBM);
     g.tiles_n = tiles(g.b, g.N, BN);
-    g.group_m = 16;
+    g.group_m = env_int("TFB_TC_GROUP_M", 16);
+    g.elect = env_int("TFB_TC_ELECT", 1);
     const int64_t grid = g.tiles_m * g.tiles_n * g.B;
     if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
     LaunchScope ls(ctx, "contract_tf32x3");
