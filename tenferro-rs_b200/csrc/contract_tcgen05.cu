@@ -62,6 +62,7 @@ struct TcArgs {
     int64_t tiles_m, tiles_n;
     int group_m;                  // m-tiles per raster group (L2 reuse)
     int elect;                    // 1: one lane per warp polls/arrives on mbarriers
+    int raw_big;                  // 1: leave the raw tile in place as the big operand (hardware truncation)
     int* status;
 };
 
@@ -311,9 +312,21 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             for (int c = t; c < CHUNKS; c += kSplitThreads) {
                 float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
                 float4 b, sm;
-                b.x = to_tf32(v.x); b.y = to_tf32(v.y); b.z = to_tf32(v.z); b.w = to_tf32(v.w);
-                sm.x = v.x - b.x; sm.y = v.y - b.y; sm.z = v.z - b.z; sm.w = v.w - b.w;
-                *reinterpret_cast<float4*>(big + (size_t)c * 16) = b;
+                if (g.raw_big) {
+                    // the tensor core reads only the upper 19 bits of each f32: the raw tile
+                    // already is the truncated "big" operand, nothing to write back
+                    b.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+                    b.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+                    b.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+                    b.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+                } else {
+                    b.x = to_tf32(v.x); b.y = to_tf32(v.y); b.z = to_tf32(v.z); b.w = to_tf32(v.w);
+                    *reinterpret_cast<float4*>(big + (size_t)c * 16) = b;
+                }
+                // the remainder is exact in f32; rounding it to tf32 here keeps the hardware's
+                // truncation of it from adding a one-sided error
+                sm.x = to_tf32(v.x - b.x); sm.y = to_tf32(v.y - b.y);
+                sm.z = to_tf32(v.z - b.z); sm.w = to_tf32(v.w - b.w);
                 *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
             }
             fence_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
@@ -476,6 +489,7 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     g.tiles_n = tiles(g.b, g.N, BN);
     g.group_m = env_int("TFB_TC_GROUP_M", 16);
     g.elect = env_int("TFB_TC_ELECT", 1);
+    g.raw_big = env_int("TFB_TC_RAWBIG", 1);
     const int64_t grid = g.tiles_m * g.tiles_n * g.B;
     if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
     LaunchScope ls(ctx, "contract_tf32x3");
