@@ -473,8 +473,8 @@ def wl_grouped(env: Env):
     return {
         "metric": "einsum GFLOP/s (grouped 'bij,bjk->bik', f32, ragged)", "unit": "GFLOP/s", "dtype": "f32",
         "scaling": "strong", "step": step, "work": flops_all, "read_result": read_result, "e2e_step": None, "h2d": 0,
-        "d2h": 0, "kernel": "grouped_tf32x3", "kernels_any": ["grouped_tf32x3", "grouped_simt"],
-        "kernel_label": "grouped_tf32x3_kernel (persistent, atomic ticket, mma.sync 3xTF32)",
+        "d2h": 0, "kernel": "grouped_tf32x3", "kernels_any": ["grouped_fma", "grouped_tf32x3", "grouped_simt"],
+        "kernel_label": "grouped_f32_kernel (persistent CTAs, host-built stage table, double-buffered cp.async panels)",
         "per_launch": float(bytes_p[lo:hi].sum()), "bound": "hbm",
         "peak": (lambda: hbm) if hbm else ctx.probe_hbm_gbs,
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if hbm else "library copy probe (MEASURED_PEAKS.json absent)",

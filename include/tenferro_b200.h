@@ -284,6 +284,15 @@ typedef struct tfb_gemm_problem {
 /* `problems` is a HOST array; it is copied to the device by this call. */
 tfb_status tfb_grouped_gemm(tfb_ctx* ctx, int32_t dtype, size_t n_problems, const tfb_gemm_problem* problems,
                             const void* alpha, const void* beta);
+/* The same in the plan/execute form of `TensorPrims` (tenferro-prims/src/lib.rs:284-320): the
+ * table is validated, cut into tiles and copied to the device once; every execute is then a
+ * single launch with no host-side table work.  The plan keeps the pointers of the table, so
+ * the operand buffers must stay where they are while the plan is used. */
+typedef struct tfb_grouped_plan tfb_grouped_plan;
+tfb_status tfb_grouped_plan_create(tfb_ctx* ctx, int32_t dtype, size_t n_problems, const tfb_gemm_problem* problems,
+                                   tfb_grouped_plan** out);
+tfb_status tfb_grouped_plan_execute(tfb_grouped_plan* plan, const void* alpha, const void* beta);
+void tfb_grouped_plan_destroy(tfb_grouped_plan* plan);
 
 /* ------------------------------------------------------------------ */
 /* tenferro-einsum: Subscripts, ContractionTree, executor              */

@@ -176,11 +176,6 @@ tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined)
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 tfb_status contract_c32_3m(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 
-tfb_status grouped_tf32_fast(tfb_ctx* ctx, size_t n, const tfb_gemm_problem* problems, Scalar alpha, Scalar beta,
-                             bool* declined);
-tfb_status grouped_gemm_launch(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, Scalar alpha,
-                               Scalar beta);
-
 // Scratch from the context pool, released stream-ordered when the object dies.
 struct PoolBlock {
     tfb_ctx* ctx = nullptr;
@@ -188,6 +183,17 @@ struct PoolBlock {
     ~PoolBlock();
     tfb_status alloc(tfb_ctx* c, size_t bytes);
 };
+
+// Device-resident schedule of one problem table for the tensor-core grouped kernel.
+struct GroupedFast {
+    PoolBlock mem;
+    int64_t total_units = 0;
+    int grid = 0;
+};
+tfb_status grouped_tf32_prepare(tfb_ctx* ctx, size_t n, const tfb_gemm_problem* problems, GroupedFast* out,
+                                bool* declined);
+tfb_status grouped_tf32_run(tfb_ctx* ctx, const GroupedFast& f, Scalar alpha, Scalar beta, bool* declined);
+tfb_status grouped_simt(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, Scalar alpha, Scalar beta);
 
 int env_int(const char* name, int dflt);
 

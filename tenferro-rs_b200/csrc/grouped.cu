@@ -148,25 +148,86 @@ tfb_status grouped_simt(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_proble
     return TFB_OK;
 }
 
-tfb_status grouped_gemm_launch(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, Scalar alpha,
-                               Scalar beta) {
+}  // namespace tfb
+
+// A problem table prepared once: the tensor-core schedule on the device when the table
+// qualifies, else the host copy of the table for the SIMT kernel.
+struct tfb_grouped_plan {
+    tfb_ctx* ctx = nullptr;
+    int dtype = 0;
+    bool fast = false;
+    tfb::GroupedFast schedule;
+    std::vector<tfb_gemm_problem> problems;
+};
+
+namespace {
+
+tfb_status prepare(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* problems, tfb_grouped_plan* plan) {
+    using namespace tfb;
     DeviceGuard g(ctx->device);
+    plan->ctx = ctx;
+    plan->dtype = dtype;
+    plan->problems.assign(problems, problems + n);
     if (dtype == TFB_F32) {
         bool declined = true;
-        TFB_TRY(grouped_tf32_fast(ctx, n, problems, alpha, beta, &declined));
-        if (!declined) return TFB_OK;
+        TFB_TRY(grouped_tf32_prepare(ctx, n, problems, &plan->schedule, &declined));
+        plan->fast = !declined;
     }
-    return grouped_simt(ctx, dtype, n, problems, alpha, beta);
+    return TFB_OK;
 }
 
-}  // namespace tfb
+tfb_status run(tfb_grouped_plan* plan, tfb::Scalar alpha, tfb::Scalar beta) {
+    using namespace tfb;
+    DeviceGuard g(plan->ctx->device);
+    if (plan->fast) {
+        bool declined = true;
+        TFB_TRY(grouped_tf32_run(plan->ctx, plan->schedule, alpha, beta, &declined));
+        if (!declined) return TFB_OK;
+    }
+    return grouped_simt(plan->ctx, plan->dtype, plan->problems.size(), plan->problems.data(), alpha, beta);
+}
+
+tfb_status check_args(const char* who, tfb_ctx* ctx, int32_t dtype, size_t n, const tfb_gemm_problem* problems) {
+    using namespace tfb;
+    if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", who);
+    if (!dtype_valid(dtype)) return fail(TFB_ERR_INVALID_ARGUMENT, "unknown dtype %d", (int)dtype);
+    if (n && !problems) return fail(TFB_ERR_INVALID_ARGUMENT, "%s: problems is NULL", who);
+    return TFB_OK;
+}
+
+}  // namespace
 
 extern "C" tfb_status tfb_grouped_gemm(tfb_ctx* ctx, int32_t dtype, size_t n_problems, const tfb_gemm_problem* problems,
                                        const void* alpha, const void* beta) {
     using namespace tfb;
-    if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_grouped_gemm: ctx is NULL");
-    if (!dtype_valid(dtype)) return fail(TFB_ERR_INVALID_ARGUMENT, "unknown dtype %d", (int)dtype);
-    if (n_problems && !problems) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_grouped_gemm: problems is NULL");
+    TFB_TRY(check_args("tfb_grouped_gemm", ctx, dtype, n_problems, problems));
     if (!alpha || !beta) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_grouped_gemm: alpha/beta are NULL");
-    return grouped_gemm_launch(ctx, dtype, n_problems, problems, load_scalar(dtype, alpha), load_scalar(dtype, beta));
+    tfb_grouped_plan plan;
+    TFB_TRY(prepare(ctx, dtype, n_problems, problems, &plan));
+    return run(&plan, load_scalar(dtype, alpha), load_scalar(dtype, beta));
 }
+
+extern "C" tfb_status tfb_grouped_plan_create(tfb_ctx* ctx, int32_t dtype, size_t n_problems,
+                                              const tfb_gemm_problem* problems, tfb_grouped_plan** out) {
+    using namespace tfb;
+    TFB_TRY(check_args("tfb_grouped_plan_create", ctx, dtype, n_problems, problems));
+    if (!out) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_grouped_plan_create: out is NULL");
+    auto* plan = new (std::nothrow) tfb_grouped_plan;
+    if (!plan) return fail(TFB_ERR_DEVICE, "out of host memory");
+    const tfb_status st = prepare(ctx, dtype, n_problems, problems, plan);
+    if (st != TFB_OK) {
+        delete plan;
+        return st;
+    }
+    *out = plan;
+    return TFB_OK;
+}
+
+extern "C" tfb_status tfb_grouped_plan_execute(tfb_grouped_plan* plan, const void* alpha, const void* beta) {
+    using namespace tfb;
+    if (!plan) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_grouped_plan_execute: plan is NULL");
+    if (!alpha || !beta) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_grouped_plan_execute: alpha/beta are NULL");
+    return run(plan, load_scalar(plan->dtype, alpha), load_scalar(plan->dtype, beta));
+}
+
+extern "C" void tfb_grouped_plan_destroy(tfb_grouped_plan* plan) { delete plan; }

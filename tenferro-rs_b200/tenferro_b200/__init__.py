@@ -33,5 +33,7 @@ from .einsum import (  # noqa: F401
     einsum_with_subscripts_into,
     einsum_with_subscripts_owned,
 )
-from .prims import ContractKernel, CudaBackend, CudaPlan, Extension, PrimDescriptor, ReduceOp, grouped_gemm  # noqa: F401
+from .prims import (  # noqa: F401
+    ContractKernel, CudaBackend, CudaPlan, Extension, PreparedGroupedGemm, PrimDescriptor, ReduceOp, grouped_gemm,
+)
 from .tensor import MemoryOrder, Tensor  # noqa: F401

@@ -112,6 +112,9 @@ PROTOTYPES = {
         C.c_int, [_VP, C.c_int32, C.c_int32, c_u32_p, C.c_size_t, C.POINTER(TfbView), c_u32_p, C.c_size_t,
                   C.POINTER(TfbView), _VP, _VP]),
     "tfb_grouped_gemm": (C.c_int, [_VP, C.c_int32, C.c_size_t, C.POINTER(TfbGemmProblem), _VP, _VP]),
+    "tfb_grouped_plan_create": (C.c_int, [_VP, C.c_int32, C.c_size_t, C.POINTER(TfbGemmProblem), C.POINTER(_VP)]),
+    "tfb_grouped_plan_execute": (C.c_int, [_VP, _VP, _VP]),
+    "tfb_grouped_plan_destroy": (None, [_VP]),
     "tfb_subscripts_new": (C.c_int, [C.c_size_t, c_size_p, C.POINTER(c_u32_p), C.c_size_t, c_u32_p, _VPP]),
     "tfb_subscripts_parse": (C.c_int, [C.c_char_p, _VPP]),
     "tfb_subscripts_destroy": (C.c_int, [_VP]),

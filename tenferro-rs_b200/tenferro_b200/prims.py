@@ -197,20 +197,31 @@ class CudaBackend:
 
 
 class PreparedGroupedGemm:
-    """A problem table marshalled once, for loops that run the same ragged batch repeatedly."""
+    """A problem table prepared once (tfb_grouped_plan_*): validated, cut into tiles and copied
+    to the device at construction; `run` is then one launch.  The operand buffers the table
+    points to must stay alive and in place while the object is used."""
 
     def __init__(self, problems, dtype, alpha=1.0, beta=0.0, ctx: Optional[Context] = None):
         self.ctx = ctx or Context.get(0)
         problems = list(problems)
         self.n = len(problems)
-        self.arr = (_lib.TfbGemmProblem * max(self.n, 1))()
+        arr = (_lib.TfbGemmProblem * max(self.n, 1))()
         for i, p in enumerate(problems):
-            self.arr[i] = _lib.TfbGemmProblem(*p)
-        self.code = dtype_code(dtype)
+            arr[i] = _lib.TfbGemmProblem(*p)
         self.alpha, self.beta = scalar_arg(alpha, dtype), scalar_arg(beta, dtype)
+        self.handle = C.c_void_p()
+        check(lib.tfb_grouped_plan_create(self.ctx.handle, dtype_code(dtype), self.n, arr, C.byref(self.handle)))
 
     def run(self) -> None:
-        check(lib.tfb_grouped_gemm(self.ctx.handle, self.code, self.n, self.arr, self.alpha, self.beta))
+        check(lib.tfb_grouped_plan_execute(self.handle, self.alpha, self.beta))
+
+    def __del__(self):
+        try:
+            if self.handle:
+                lib.tfb_grouped_plan_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
 
 
 def grouped_gemm(problems, dtype, alpha=1.0, beta=0.0, ctx: Optional[Context] = None) -> None:

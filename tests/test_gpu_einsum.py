@@ -231,6 +231,31 @@ def test_config3_grouped_sample(tb, oracle, golden):
         assert oracle.rel_frobenius(got, golden[f"cfg3_out{p}"]) <= 1e-5
 
 
+@pytest.mark.parametrize("odd", [False, True])
+def test_grouped_plan_runs_twice_with_accumulate(tb, oracle, odd):
+    """The prepared form of the grouped product: C_p = alpha A_p B_p + beta C_p, executed twice on
+    the same table (the second run accumulates onto the first).  `odd` adds a problem whose
+    dims are not multiples of 16, which sends the whole table to the SIMT kernel."""
+    table = [tuple(r) for r in oracle.grouped_table(3100, 40)]
+    if odd:
+        table.append((7, 13, 5))
+    held, probs, ab = [], [], []
+    for p, (i, j, k) in enumerate(table):
+        a, b = oracle.uniform(3101 + 2 * p, (i, j), np.float32), oracle.uniform(3102 + 2 * p, (j, k), np.float32)
+        c0 = oracle.uniform(3900 + p, (i, k), np.float32)
+        ta, tb_, tc = tb.Tensor.from_numpy(a), tb.Tensor.from_numpy(b), tb.Tensor.from_numpy(c0)
+        held += [ta, tb_, tc]
+        probs.append((i, k, j, ta._block.ptr, 1, i, tb_._block.ptr, 1, j, tc._block.ptr, 1, i))
+        ab.append((oracle.np_batched_gemm(a, b), c0.astype(np.float64)))
+    plan = tb.PreparedGroupedGemm(probs, np.float32, alpha=0.5, beta=-2.0)
+    plan.run()
+    plan.run()
+    tb.Context.get(0).synchronize()
+    for p, (prod, c0) in enumerate(ab):
+        want = 0.5 * prod - 2.0 * (0.5 * prod - 2.0 * c0)
+        assert oracle.rel_frobenius(held[3 * p + 2].to_numpy(), want) <= 1e-5, p
+
+
 def test_config4_network_dim24(tb, oracle):
     """'ijk,jlm,kmn,lnp->ip', complex64, N(0,1) parts, every index 24 (96 in the benchmark)."""
     ops = [oracle.normal(4000 + i, (24, 24, 24), np.complex64) for i in range(4)]
