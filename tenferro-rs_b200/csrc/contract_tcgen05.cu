@@ -103,6 +103,14 @@ __device__ __forceinline__ float to_tf32(float x) {
     return __uint_as_float(u);
 }
 
+// a - trunc_tf32(a), exact in f32, plus half a TF32 ulp so that the tensor core's truncation of
+// it rounds to nearest.  Integer operations only: conversion instructions run at a fraction
+// of the ALU rate.
+__device__ __forceinline__ float remainder_rounded(float a) {
+    const float r = a - __uint_as_float(__float_as_uint(a) & 0xffffe000u);
+    return __uint_as_float(__float_as_uint(r) + 0x1000u);
+}
+
 constexpr int kChunk = 4;           // k-blocks accumulated inside TMEM before promotion (K = 128)
 constexpr int kSplitThreads = 256;  // warps 2..9
 
@@ -325,8 +333,13 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
                 // the remainder is exact in f32; rounding it to tf32 here keeps the hardware's
                 // truncation of it from adding a one-sided error
-                sm.x = to_tf32(v.x - b.x); sm.y = to_tf32(v.y - b.y);
-                sm.z = to_tf32(v.z - b.z); sm.w = to_tf32(v.w - b.w);
+                if (g.raw_big) {
+                    sm.x = remainder_rounded(v.x); sm.y = remainder_rounded(v.y);
+                    sm.z = remainder_rounded(v.z); sm.w = remainder_rounded(v.w);
+                } else {
+                    sm.x = to_tf32(v.x - b.x); sm.y = to_tf32(v.y - b.y);
+                    sm.z = to_tf32(v.z - b.z); sm.w = to_tf32(v.w - b.w);
+                }
                 *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
             }
             fence_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
@@ -362,6 +375,274 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ CTA-pair variant
+// Two CTAs of a cluster share one 256 x 256 tile of C through tcgen05.mma.cta_group::2: each
+// CTA stages its own 128 rows of A and only HALF of the B tile (128 of the 256 columns), the
+// pair's tensor cores exchange the B halves, and each CTA ends up with its 128 x 256 part of
+// the product in its own tensor memory.  Per k-block a CTA moves a third less through shared
+// memory than the single-CTA kernel (which is bound by exactly that), in 64 KB stages instead
+// of 96 KB, so three stages fit.
+//
+// Roles per CTA are those of the single-CTA kernel, except that only the leader (rank 0)
+// issues MMAs.  Barriers:
+//   full[s]      own CTA   TMA bytes of stage s landed                     -> own converters
+//   split[s]     LEADER    both CTAs' converters are done with stage s     -> MMA thread
+//   empty[s]     each CTA  MMAs that read stage s retired (commit to both) -> own producer
+//   chunk[b]     each CTA  work accumulator b complete (commit to both)    -> own converters
+//   promoted[b]  LEADER    both CTAs have read work accumulator b          -> MMA thread
+// Arrivals on the leader's barriers from the other CTA are cluster-scope releases on the mapped
+// address; commits go to each CTA's barrier by its own instruction, so no instruction here
+// is a multicast.
+struct PairCfg {
+    static constexpr int BN = 256;                  // tile columns of the pair
+    static constexpr int A_BYTES = kBM * kBK * 4;   // 16 KB: this CTA's 128 rows
+    static constexpr int B_BYTES = 128 * kBK * 4;   // 16 KB: this CTA's 128 of the 256 columns
+    static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
+    static constexpr int STAGES = 3;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int COLS_PER_WARP = BN / 2;
+    static_assert(kChunk >= STAGES, "promotion lag assumes a chunk spans at least the ring");
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + kSplitThreads, 1)
+contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
+    using Cfg = PairCfg;
+    constexpr int STAGES = Cfg::STAGES, BN = Cfg::BN, CPW = Cfg::COLS_PER_WARP;
+    extern __shared__ char smem_raw[];
+    // Both CTAs must lay their rings out identically: descriptors and barrier offsets are
+    // interpreted in each CTA's own shared memory.  The dynamic segment starts at the same
+    // offset in every CTA of a launch, so the same rounding gives the same layout.
+    char* smem = (char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t ring = smem_u32(smem);
+    const uint32_t bars = ring + STAGES * Cfg::STAGE_BYTES;
+    auto bar_full = [&](int s) { return bars + 8u * s; };
+    auto bar_split = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto bar_empty = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+    auto bar_chunk = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+    auto bar_promoted = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+    const uint32_t tmem_word = bars + 8u * (3 * STAGES + 4);
+    volatile uint32_t* tmem_word_ptr = (volatile uint32_t*)(smem + STAGES * Cfg::STAGE_BYTES + 8 * (3 * STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    constexpr int kWarps = kSplitThreads / 32;
+
+    // Pair tile: 128-row m-tiles 2 tmp, 2 tmp + 1 (one per CTA) x 128-column n-tiles 2 tnp, 2 tnp + 1.
+    const int64_t tiles_mp = (g.tiles_m + 1) / 2, tiles_np = (g.tiles_n + 1) / 2;
+    int64_t tile = blockIdx.x >> 1;
+    const int64_t tiles_per_batch = tiles_mp * tiles_np;
+    const int64_t bb = tile / tiles_per_batch;
+    tile -= bb * tiles_per_batch;
+    const int64_t group_sz = (int64_t)g.group_m * tiles_np;
+    const int64_t grp = tile / group_sz;
+    const int64_t first_m = grp * g.group_m;
+    const int64_t rows_in_group = min((int64_t)g.group_m, tiles_mp - first_m);
+    const int64_t in_grp = tile - grp * group_sz;
+    const int64_t tmp = first_m + in_grp % rows_in_group;
+    const int64_t tnp = in_grp / rows_in_group;
+    // A tile past the end (odd tile counts) has coordinates outside the tensor: TMA fills it
+    // with zeros and nothing of it is stored.
+    TileRows tr_m = tile_rows(g.a, 2 * tmp + rank, kBM, g.M);
+    if (2 * tmp + rank >= g.tiles_m) tr_m.valid = 0;
+    TileRows tr_n[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        tr_n[h] = tile_rows(g.b, 2 * tnp + h, 128, g.N);
+        if (2 * tnp + h >= g.tiles_n) tr_n[h].valid = 0;
+    }
+    const TileRows tr_nl = rank ? tr_n[1] : tr_n[0];  // the half of B this CTA stages
+    const int num_kb = g.num_kb;
+    const int num_chunks = (num_kb + kChunk - 1) / kChunk;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_split(s), 2 * kWarps);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_chunk(b), 1);
+            mbar_init(bar_promoted(b), 2 * kWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_word, Cfg::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();  // barriers of both CTAs exist before anyone arrives on the peer's
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_word_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (each CTA its own tiles)
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t use = kb / STAGES;
+                mbar_wait(bar_empty(s), (use & 1) ^ 1, g.status, 0x111);
+                const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
+                const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+                mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
+                const int k2 = kb / g.k_blocks1, k1 = (kb - k2 * g.k_blocks1) * kBK;
+                if (g.a.mn_major) {
+                    for (int c = 0; c < kBM / 32; ++c) {
+                        int f1 = tr_m.f1 + 32 * c, f2 = tr_m.f2;
+                        if (g.a.pack) {
+                            const int64_t row = tr_m.base + 32 * c;
+                            f2 = (int)(row / g.a.e1);
+                            f1 = (int)(row - (int64_t)f2 * g.a.e1);
+                        }
+                        tma_load_5d(a_dst + c * 4096, &map_a, bar_full(s), f1, f2, k1, k2, (int)bb);
+                    }
+                } else {
+                    tma_load_5d(a_dst, &map_a, bar_full(s), k1, k2, tr_m.f1, tr_m.f2, (int)bb);
+                }
+                if (g.b.mn_major) {
+                    for (int c = 0; c < 128 / 32; ++c) {
+                        int f1 = tr_nl.f1 + 32 * c, f2 = tr_nl.f2;
+                        if (g.b.pack) {
+                            const int64_t row = tr_nl.base + 32 * c;
+                            f2 = (int)(row / g.b.e1);
+                            f1 = (int)(row - (int64_t)f2 * g.b.e1);
+                        }
+                        tma_load_5d(b_dst + c * 4096, &map_b, bar_full(s), f1, f2, k1, k2, (int)bb);
+                    }
+                } else {
+                    tma_load_5d(b_dst, &map_b, bar_full(s), k1, k2, tr_nl.f1, tr_nl.f2, (int)bb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)g.a.mn_major << 15) |
+                                   ((uint32_t)g.b.mn_major << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)((2 * kBM) >> 4) << 24);
+            const uint32_t a_lbo = g.a.mn_major ? 4096u : 16u, b_lbo = g.b.mn_major ? 4096u : 16u;
+            const uint32_t a_sbo = g.a.mn_major ? 512u : 1024u, b_sbo = g.b.mn_major ? 512u : 1024u;
+            const uint32_t a_lay = g.a.mn_major ? 1u : 2u, b_lay = g.b.mn_major ? 1u : 2u;
+            const uint32_t a_step = g.a.mn_major ? 1024u : 32u, b_step = g.b.mn_major ? 1024u : 32u;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t use = kb / STAGES;
+                const int chunk = kb / kChunk, buf = chunk & 1;
+                const bool chunk_first = kb % kChunk == 0;
+                const bool chunk_last = (kb % kChunk == kChunk - 1) || kb == num_kb - 1;
+                if (chunk_first && chunk >= 2) {
+                    mbar_wait_cluster(bar_promoted(buf), ((uint32_t)(chunk >> 1) - 1) & 1, g.status, 0x115);
+                    tc_fence_after();
+                }
+                mbar_wait_cluster(bar_split(s), use & 1, g.status, 0x112);
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t a_big = ring + s * Cfg::STAGE_BYTES;
+                const uint32_t b_big = a_big + Cfg::A_BYTES;
+                const uint32_t a_small = b_big + Cfg::B_BYTES;
+                const uint32_t b_small = a_small + Cfg::A_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < kBK / 8; ++ks) {
+                    const uint64_t da_big = smem_desc(a_big + ks * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t da_small = smem_desc(a_small + ks * a_step, a_lbo, a_sbo, a_lay);
+                    const uint64_t db_big = smem_desc(b_big + ks * b_step, b_lbo, b_sbo, b_lay);
+                    const uint64_t db_small = smem_desc(b_small + ks * b_step, b_lbo, b_sbo, b_lay);
+                    tc_mma_tf32_pair(tmem_d, da_small, db_big, idesc, !(chunk_first && ks == 0));
+                    tc_mma_tf32_pair(tmem_d, da_big, db_small, idesc, 1);
+                    tc_mma_tf32_pair(tmem_d, da_big, db_big, idesc, 1);
+                }
+                tc_commit_pair(bar_empty(s));
+                tc_commit_pair(map_to_cta(bar_empty(s), 1));
+                if (chunk_last) {
+                    tc_commit_pair(bar_chunk(buf));
+                    tc_commit_pair(map_to_cta(bar_chunk(buf), 1));
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- split + promote, then epilogue
+        const int t = threadIdx.x - 64;
+        const int lane_grp = warp & 3;
+        const int half = (warp - 2) >> 2;  // which 128 columns of the tile this warp reads back
+        const int col0 = half * CPW;
+        const uint32_t tmem_mine = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)col0;
+        const uint32_t leader_split0 = map_to_cta(bar_split(0), 0), leader_promoted0 = map_to_cta(bar_promoted(0), 0);
+        float acc[CPW];
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) acc[j] = 0.f;
+        int next_promote = 0;
+        auto promote = [&](int chunk) {
+            const int buf = chunk & 1;
+            if (lane == 0) mbar_wait(bar_chunk(buf), (uint32_t)(chunk >> 1) & 1, g.status, 0x114);
+            __syncwarp();
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < CPW; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(tmem_mine + (uint32_t)(buf * BN + c0), r);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_promoted0 + 8u * buf);
+        };
+        for (int kb = 0; kb < num_kb; ++kb) {
+            const int s = kb % STAGES;
+            const uint32_t use = kb / STAGES;
+            if (lane == 0) mbar_wait(bar_full(s), use & 1, g.status, 0x113);
+            __syncwarp();
+            char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
+            char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
+            constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
+#pragma unroll 4
+            for (int c = t; c < CHUNKS; c += kSplitThreads) {
+                const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
+                float4 sm;
+                // raw tile = truncated big operand; remainder exact, rounded to tf32
+                sm.x = remainder_rounded(v.x);
+                sm.y = remainder_rounded(v.y);
+                sm.z = remainder_rounded(v.z);
+                sm.w = remainder_rounded(v.w);
+                *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_split0 + 8u * s);
+            while (next_promote < num_chunks &&
+                   min((next_promote + 1) * kChunk, num_kb) - 1 + STAGES <= kb)
+                promote(next_promote++);
+        }
+        while (next_promote < num_chunks) promote(next_promote++);
+
+        const int row = lane_grp * 32 + lane;
+        const TileRows trn = half ? tr_n[1] : tr_n[0];
+        if (row < tr_m.valid) {
+            float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
+            const int64_t cm = g.c_m[tr_m.base + row];
+            const bool read_c = g.beta != 0.f;
+#pragma unroll
+            for (int j = 0; j < CPW; ++j) {
+                if (j < trn.valid) {
+                    float* p = C + cm + g.c_n[trn.base + j];
+                    float v = g.alpha * acc[j];
+                    if (read_c) v += g.beta * *p;
+                    *p = v;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still reach into it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
     }
 }
 
@@ -498,6 +779,38 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     return TFB_OK;
 }
 
+tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcArgs g) {
+    using Cfg = PairCfg;
+    static std::mutex mu;
+    static std::map<int, bool> configured;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[ctx->device]) {
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg::SMEM_BYTES));
+            configured[ctx->device] = true;
+        }
+    }
+    g.a = a.geom;
+    g.b = b.geom;
+    auto tiles = [](const TcGeom& o, int64_t total, int rows) -> int64_t {
+        if (o.pack) return (total + rows - 1) / rows;
+        return (total / o.e1) * o.tiles1;
+    };
+    g.tiles_m = tiles(g.a, g.M, kBM);  // 128-row tiles; a pair takes two of each
+    g.tiles_n = tiles(g.b, g.N, 128);
+    g.group_m = env_int("TFB_TC_GROUP_M", 8);
+    g.elect = 1;
+    g.raw_big = 1;
+    const int64_t grid = 2 * ((g.tiles_m + 1) / 2) * ((g.tiles_n + 1) / 2) * g.B;
+    if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
+    LaunchScope ls(ctx, "contract_tf32x3");
+    // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
+    contract_tf32x3_pair_kernel<<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+    TFB_CUDA(cudaGetLastError());
+    return TFB_OK;
+}
+
 // Peak probe: one CTA per SM issues 128 x 256 x 8 TF32 MMAs back to back on operand tiles
 // that stay in shared memory; nothing else runs.  The quotient is the dense TF32 rate the
 // tensor pipe sustains, the denominator for "fraction of TF32 peak" (a 3xTF32 contraction
@@ -579,8 +892,10 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     if (M < 32 || N < 32 || K < 8) return TFB_OK;
     if (M > INT32_MAX - 256 || N > INT32_MAX - 256 || K > INT32_MAX - 64) return TFB_OK;
     const int bn = (N >= 256 && env_int("TFB_TC_BN", 256) == 256) ? 256 : 128;
+    // Pairs of CTAs on 256 x 256 tiles when the output has room for them.
+    const bool pair = bn == 256 && M >= 256 && env_int("TFB_TC_PAIR", 1);
     OperandMap a = make_operand_map(p, p.m, 0, p.a, kBM);
-    OperandMap b = make_operand_map(p, p.n, 1, p.b, bn);
+    OperandMap b = make_operand_map(p, p.n, 1, p.b, pair ? 128 : bn);
     if (!a.ok || !b.ok) return TFB_OK;
     std::shared_ptr<ContractTables> t;
     TFB_TRY(get_tables(ctx, p, &t));
@@ -597,6 +912,7 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     g.num_kb = (int)((K / g.k_e1) * g.k_blocks1);
     g.status = ctx->dev_status;
     *declined = false;
+    if (pair) return launch_tc_pair(ctx, a, b, g);
     return bn == 256 ? launch_tc<256>(ctx, a, b, g) : launch_tc<128>(ctx, a, b, g);
 }
 
