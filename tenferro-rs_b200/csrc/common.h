@@ -173,7 +173,8 @@ tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_ker
 // Family-specific launchers (each may decline with *declined = true and TFB_OK).
 tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p);
 tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
-tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
+tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined,
+                            const int64_t* const* c_tables = nullptr);
 tfb_status contract_c32_3m(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 
 // Scratch from the context pool, released stream-ordered when the object dies.

@@ -1,16 +1,23 @@
-// Complex32 contraction on the tensor cores: three real 3xTF32 products (the "3M" scheme)
-// around the f32 tcgen05 kernel.
+// Complex32 contraction on the tensor cores as ONE real 3xTF32 product.
 //
-//   P1 = Ar Br,  P2 = Ai Bi,  P3 = (Ar + Ai)(Br + Bi)
-//   Re C = P1 - P2,   Im C = P3 - P1 - P2
+// A complex product is a real product of doubled extents:
 //
-// A gather kernel reads the interleaved operands through the offset tables (any strides, conj
-// folded in as a sign) and writes the three real planes of each operand K-major, the layout
-// the tensor-core kernel streams fastest; a scatter kernel combines the three products,
-// applies alpha/beta in complex arithmetic and writes the interleaved output through the C
-// tables.  The planes and products live in pool scratch for the duration of the call.
-// One fewer product than the textbook four; the subtraction in Im C costs about a factor
-// of three in rounding error, which 3xTF32 (1e-6) has to spare against the 1e-5 tolerance.
+//   [ Re C ]   [ Re A  -Im A ] [ Re B ]
+//   [ Im C ] = [ Im A   Re A ] [ Im B ]
+//
+// With the real and imaginary parts interleaved along the rows of C' (row 2m + c), along K of
+// both operands (column 2k + c) this reads  C' (2M x N) = A' (2M x 2K) B' (2K x N),  where
+//   * C' is the complex output itself, seen as f32: element (m, n) part c lives at float offset
+//     2 * offset(m, n) + c, which the kernel's per-row / per-column offset tables express for
+//     ANY output strides - so the product is written straight into C, with no planes to recombine;
+//   * B' (stored K-major, [n][2k + c]) is the complex operand copied with K fastest - or, when
+//     B already has unit stride along a single contracted mode and no conjugation, B itself;
+//   * A' is built once by a gather kernel ([2m + c'][2k + c], K-major) with conjugation and the
+//     complex alpha folded in.
+// Four real products' worth of MMAs instead of the three of the 3M scheme, but no product
+// planes (3 x M x N floats written and read again), no cancellation in the imaginary part, and
+// one launch of the f32 kernel whatever the output layout.  A complex beta that is not real is
+// applied by scaling C first.
 //
 // Semantics: PrimDescriptor::{Contract, BatchedGemm} for Complex32,
 // tenferro-prims/src/lib.rs:156-168, 227-239.
@@ -21,25 +28,27 @@ namespace tfb {
 
 namespace {
 
-struct PackArgs {
+struct EmbedArgs {
     const float2* src;
     const int64_t* row_tab;  // a_m or b_n
     const int64_t* k_tab;
     const int64_t* b_tab;
-    int64_t rows, K, Kp, B;
-    int src_kfast, conj;
-    float* re;
-    float* im;
-    float* sum;
+    int64_t rows, K, B;
+    int64_t ld;              // floats per output row (>= 2K, multiple of 4)
+    int src_kfast, conj, embed;
+    float2 alpha;
+    float* dst;              // embed: [B][2 rows][ld], else [B][rows][ld]
 };
 
 // 32 x 32 (rows x k) patches through shared memory: reads follow the source's unit stride,
-// writes follow k.
-__global__ void __launch_bounds__(256) pack_planes_kernel(PackArgs g) {
+// writes follow k.  embed = 1 writes the 2 x 2 real block of alpha * op(a) per element (two
+// output rows), embed = 0 the element itself.
+__global__ void __launch_bounds__(256) embed_operand_kernel(EmbedArgs g) {
     __shared__ float2 tile[32][33];
     const int64_t tiles_r = (g.rows + 31) / 32, tiles_k = (g.K + 31) / 32;
     const int64_t n_tiles = tiles_r * tiles_k * g.B;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const int64_t kpad = g.ld / 2;  // complex columns per output row, zero-filled past K
     for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
         const int64_t tr = t % tiles_r, rest = t / tiles_r, tk = rest % tiles_k, b = rest / tiles_k;
         const int64_t r0 = tr * 32, k0 = tk * 32;
@@ -54,48 +63,54 @@ __global__ void __launch_bounds__(256) pack_planes_kernel(PackArgs g) {
         __syncthreads();
         for (int j = ty; j < 32; j += 8) {
             const int64_t r = r0 + j, k = k0 + tx;
-            if (r < g.rows && k < g.Kp) {
+            if (r < g.rows && k < kpad) {
                 float2 v = (k < g.K) ? tile[j][tx] : make_float2(0.f, 0.f);
                 if (g.conj) v.y = -v.y;
-                const int64_t o = (b * g.rows + r) * g.Kp + k;
-                g.re[o] = v.x;
-                g.im[o] = v.y;
-                g.sum[o] = v.x + v.y;
+                if (g.embed) {
+                    const float2 w = make_float2(g.alpha.x * v.x - g.alpha.y * v.y, g.alpha.x * v.y + g.alpha.y * v.x);
+                    float* o = g.dst + ((b * g.rows + r) * 2) * g.ld + 2 * k;
+                    *reinterpret_cast<float2*>(o) = make_float2(w.x, -w.y);         // row 2r:     Re, -Im
+                    *reinterpret_cast<float2*>(o + g.ld) = make_float2(w.y, w.x);   // row 2r + 1: Im,  Re
+                } else {
+                    *reinterpret_cast<float2*>(g.dst + (b * g.rows + r) * g.ld + 2 * k) = v;
+                }
             }
         }
         __syncthreads();
     }
 }
 
-struct UnpackArgs {
-    const float* p1;
-    const float* p2;
-    const float* p3;
-    float2* c;
-    const int64_t* c_b;
-    const int64_t* c_m;
-    const int64_t* c_n;
-    int64_t M, N, B;
-    float2 alpha, beta;
-};
+// Offset tables of C seen as f32: row 2m + c -> 2 c_m[m] + c, column n -> 2 c_n[n], batch b -> 2 c_b[b].
+__global__ void real_view_tables_kernel(const int64_t* c_m, const int64_t* c_n, const int64_t* c_b, int64_t M, int64_t N,
+                                        int64_t B, int64_t* out_m, int64_t* out_n, int64_t* out_b) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < 2 * M) out_m[i] = 2 * c_m[i >> 1] + (i & 1);
+    if (i < N) out_n[i] = 2 * c_n[i];
+    if (i < B) out_b[i] = 2 * c_b[i];
+}
 
-__global__ void __launch_bounds__(256) unpack_products_kernel(UnpackArgs g) {
-    const int64_t total = g.M * g.N * g.B;
-    const bool read_c = g.beta.x != 0.f || g.beta.y != 0.f;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+// C *= beta (complex), through the tables.
+__global__ void __launch_bounds__(256) scale_output_kernel(float2* c, const int64_t* c_b, const int64_t* c_m,
+                                                           const int64_t* c_n, int64_t M, int64_t N, int64_t B, float2 beta) {
+    const int64_t total = M * N * B, stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        const int64_t m = idx % g.M, rest = idx / g.M, n = rest % g.N, b = rest / g.N;
-        const float a = g.p1[idx], bb = g.p2[idx], s = g.p3[idx];
-        const float re = a - bb, im = s - a - bb;
-        float2* p = g.c + g.c_b[b] + g.c_m[m] + g.c_n[n];
-        float2 o = make_float2(g.alpha.x * re - g.alpha.y * im, g.alpha.x * im + g.alpha.y * re);
-        if (read_c) {
-            const float2 old = *p;
-            o.x += g.beta.x * old.x - g.beta.y * old.y;
-            o.y += g.beta.x * old.y + g.beta.y * old.x;
-        }
-        *p = o;
+        const int64_t m = idx % M, rest = idx / M, n = rest % N, b = rest / N;
+        float2* p = c + c_b[b] + c_m[m] + c_n[n];
+        const float2 o = *p;
+        *p = make_float2(beta.x * o.x - beta.y * o.y, beta.x * o.y + beta.y * o.x);
     }
+}
+
+// B can serve as B' in place when one contracted mode with unit stride carries all of K, nothing
+// is conjugated, and every other stride keeps the doubled (float) strides 16-byte aligned.
+bool b_is_real_view(const ContractProblem& p) {
+    if (p.conj_b || p.k.size() != 1 || p.k[0].s[1] != 1) return false;
+    if ((uintptr_t)p.b % 16 != 0 || p.n.size() > 2 || p.batch.size() > 1) return false;
+    for (const Mode& m : p.n)
+        if (m.extent > 1 && (m.s[1] <= 0 || (2 * m.s[1]) % 4 != 0)) return false;
+    for (const Mode& m : p.batch)
+        if (m.extent > 1 && (m.s[1] <= 0 || (2 * m.s[1]) % 4 != 0)) return false;
+    return true;
 }
 
 }  // namespace
@@ -104,64 +119,77 @@ tfb_status contract_c32_3m(tfb_ctx* ctx, const ContractProblem& p, bool* decline
     *declined = true;
     if (p.dtype != TFB_C32 || env_int("TFB_NO_TCGEN05", 0)) return TFB_OK;
     const int64_t M = p.M(), N = p.N(), K = p.K(), B = p.B();
-    if (M < 32 || N < 32 || K < 8) return TFB_OK;
-    const int64_t Kp = (K + 3) / 4 * 4;  // rows of the planes start on 16-byte boundaries
-    if (M * Kp * B > (int64_t)1 << 40 || N * Kp * B > (int64_t)1 << 40) return TFB_OK;
+    if (2 * M < 32 || N < 32 || K < 4) return TFB_OK;
+    const int64_t ld = (2 * K + 3) / 4 * 4;  // rows of the packed operands start on 16-byte boundaries
+    if (2 * M * ld * B > (int64_t)1 << 40 || N * ld * B > (int64_t)1 << 40) return TFB_OK;
     std::shared_ptr<ContractTables> t;
     TFB_TRY(get_tables(ctx, p, &t));
     ContractArgs ca;
     fill_args(p, *t, &ca);
 
-    const size_t a_plane = (size_t)(M * Kp * B), b_plane = (size_t)(N * Kp * B), c_plane = (size_t)(M * N * B);
+    const bool b_in_place = b_is_real_view(p) && env_int("TFB_C32_B_IN_PLACE", 1);
+    const size_t a_floats = (size_t)(2 * M * ld * B), b_floats = b_in_place ? 0 : (size_t)(N * ld * B);
+    const size_t tab_entries = (size_t)(2 * M + N + B);
     PoolBlock ws;
-    TFB_TRY(ws.alloc(ctx, (3 * a_plane + 3 * b_plane + 3 * c_plane) * sizeof(float) + 256));
-    float* base = (float*)ws.ptr;
-    float *ar = base, *ai = ar + a_plane, *as = ai + a_plane;
-    float *br = as + a_plane, *bi = br + b_plane, *bs = bi + b_plane;
-    float *p1 = bs + b_plane, *p2 = p1 + c_plane, *p3 = p2 + c_plane;
+    TFB_TRY(ws.alloc(ctx, (a_floats + b_floats) * sizeof(float) + tab_entries * sizeof(int64_t) + 256));
+    float* a_real = (float*)ws.ptr;
+    float* b_real = a_real + a_floats;
+    int64_t* tab_m = (int64_t*)(((uintptr_t)(b_real + b_floats) + 15) & ~(uintptr_t)15);
+    int64_t* tab_n = tab_m + 2 * M;
+    int64_t* tab_b = tab_n + N;
 
-    auto pack = [&](const void* src, const int64_t* row_tab, const int64_t* k_tab, const int64_t* b_tab, int64_t rows,
-                    int kfast, bool conj, float* re, float* im, float* sum) -> tfb_status {
-        PackArgs g{(const float2*)src, row_tab, k_tab, b_tab, rows, K, Kp, B, kfast, conj ? 1 : 0, re, im, sum};
+    auto embed = [&](const void* src, const int64_t* row_tab, const int64_t* k_tab, const int64_t* b_tab, int64_t rows,
+                     int kfast, bool conj, bool emb, float2 alpha, float* dst) -> tfb_status {
+        EmbedArgs g{(const float2*)src, row_tab, k_tab, b_tab, rows, K, B, ld, kfast, conj ? 1 : 0, emb ? 1 : 0, alpha, dst};
         const int64_t n_tiles = ((rows + 31) / 32) * ((K + 31) / 32) * B;
         const int grid = (int)std::min<int64_t>(n_tiles, (int64_t)ctx->sm_count * 16);
         LaunchScope ls(ctx, "pack_planes");
-        pack_planes_kernel<<<grid, 256, 0, ctx->stream>>>(g);
+        embed_operand_kernel<<<grid, 256, 0, ctx->stream>>>(g);
         TFB_CUDA(cudaGetLastError());
         return TFB_OK;
     };
-    TFB_TRY(pack(p.a, t->a_m, t->a_k, t->a_b, M, ca.a_kfast, p.conj_a, ar, ai, as));
-    TFB_TRY(pack(p.b, t->b_n, t->b_k, t->b_b, N, ca.b_kfast, p.conj_b, br, bi, bs));
-
-    // Three real products on the packed planes: A' [B][M][Kp] and B' [B][N][Kp] K-major, P [B][N][M].
-    auto product = [&](const float* a, const float* b, float* c) -> tfb_status {
-        ContractProblem q;
-        q.dtype = TFB_F32;
-        q.a = a; q.b = b; q.c = c;
-        q.alpha = Scalar{1.0, 0.0};
-        q.beta = Scalar{0.0, 0.0};
-        if (B > 1) q.batch.push_back(Mode{B, {M * Kp, N * Kp, M * N}});
-        q.m.push_back(Mode{M, {Kp, 0, 1}});
-        q.n.push_back(Mode{N, {0, Kp, M}});
-        q.k.push_back(Mode{K, {1, 1, 0}});
-        bool d = false;
-        TFB_TRY(contract_tcgen05(ctx, q, &d));
-        if (d) return fail(TFB_ERR_DEVICE, "internal: the packed real product was declined by the tensor-core kernel");
-        return TFB_OK;
-    };
-    TFB_TRY(product(ar, br, p1));
-    TFB_TRY(product(ai, bi, p2));
-    TFB_TRY(product(as, bs, p3));
-
-    UnpackArgs u{p1, p2, p3, (float2*)p.c, t->c_b, t->c_m, t->c_n, M, N, B,
-                 make_float2((float)p.alpha.re, (float)p.alpha.im), make_float2((float)p.beta.re, (float)p.beta.im)};
-    const int64_t blocks = (M * N * B + 255) / 256;
-    const int grid = (int)std::min<int64_t>(blocks, (int64_t)ctx->sm_count * 32);
+    const float2 alpha = make_float2((float)p.alpha.re, (float)p.alpha.im);
+    TFB_TRY(embed(p.a, t->a_m, t->a_k, t->a_b, M, ca.a_kfast, p.conj_a, true, alpha, a_real));
+    if (!b_in_place)
+        TFB_TRY(embed(p.b, t->b_n, t->b_k, t->b_b, N, ca.b_kfast, p.conj_b, false, make_float2(1.f, 0.f), b_real));
     {
-        LaunchScope ls(ctx, "unpack_products");
-        unpack_products_kernel<<<grid, 256, 0, ctx->stream>>>(u);
+        const int64_t n = std::max<int64_t>(std::max<int64_t>(2 * M, N), B);
+        real_view_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(t->c_m, t->c_n, t->c_b, M, N, B, tab_m,
+                                                                                    tab_n, tab_b);
+        count_launch();
+        TFB_CUDA(cudaGetLastError());
     }
-    TFB_CUDA(cudaGetLastError());
+    double beta = p.beta.re;
+    if (p.beta.im != 0) {
+        const int64_t blocks = (M * N * B + 255) / 256;
+        LaunchScope ls(ctx, "scale");
+        scale_output_kernel<<<(unsigned)std::min<int64_t>(blocks, (int64_t)ctx->sm_count * 32), 256, 0, ctx->stream>>>(
+            (float2*)p.c, t->c_b, t->c_m, t->c_n, M, N, B, make_float2((float)p.beta.re, (float)p.beta.im));
+        TFB_CUDA(cudaGetLastError());
+        beta = 1.0;
+    }
+
+    // The real product: A' [B][2M][ld] K-major, B' [B][N][ld] K-major (or B itself), C through the tables.
+    ContractProblem q;
+    q.dtype = TFB_F32;
+    q.a = a_real;
+    q.b = b_in_place ? p.b : (const void*)b_real;
+    q.c = p.c;
+    q.alpha = Scalar{1.0, 0.0};
+    q.beta = Scalar{beta, 0.0};
+    if (b_in_place) {
+        if (B > 1) q.batch.push_back(Mode{B, {2 * M * ld, 2 * p.batch[0].s[1], 0}});
+        for (const Mode& m : p.n) q.n.push_back(Mode{m.extent, {0, 2 * m.s[1], 0}});
+    } else {
+        if (B > 1) q.batch.push_back(Mode{B, {2 * M * ld, N * ld, 0}});
+        q.n.push_back(Mode{N, {0, ld, 0}});
+    }
+    q.m.push_back(Mode{2 * M, {ld, 0, 0}});
+    q.k.push_back(Mode{2 * K, {1, 1, 0}});
+    const int64_t* c_tables[3] = {tab_b, tab_m, tab_n};
+    bool d = false;
+    TFB_TRY(contract_tcgen05(ctx, q, &d, c_tables));
+    if (d) return fail(TFB_ERR_DEVICE, "internal: the embedded real product was declined by the tensor-core kernel");
     *declined = false;
     return TFB_OK;
 }

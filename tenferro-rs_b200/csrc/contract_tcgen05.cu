@@ -63,6 +63,8 @@ struct TcArgs {
     int group_m;                  // m-tiles per raster group (L2 reuse)
     int elect;                    // 1: one lane per warp polls/arrives on mbarriers
     int raw_big;                  // 1: leave the raw tile in place as the big operand (hardware truncation)
+    int k_split, kb_per_split;    // split-K: CTAs per output tile, k-blocks per CTA
+    float* partial;               // split-K: [tile][split][BN cols][128 rows] raw sums
     int* status;
 };
 
@@ -101,6 +103,26 @@ __device__ __forceinline__ float to_tf32(float x) {
     uint32_t u;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
     return __uint_as_float(u);
+}
+
+// Raster of output tiles: m-tiles are visited in groups of `group_m` so that CTAs running
+// together share B panels (and the A panels of the group) through L2.
+struct TileCoord {
+    int64_t batch, tm, tn;
+};
+__device__ __forceinline__ TileCoord decode_tile(int64_t tile, int64_t tiles_m, int64_t tiles_n, int group_m) {
+    TileCoord t;
+    const int64_t tiles_per_batch = tiles_m * tiles_n;
+    t.batch = tile / tiles_per_batch;
+    tile -= t.batch * tiles_per_batch;
+    const int64_t group_sz = (int64_t)group_m * tiles_n;
+    const int64_t grp = tile / group_sz;
+    const int64_t first_m = grp * group_m;
+    const int64_t rows_in_group = min((int64_t)group_m, tiles_m - first_m);
+    const int64_t in_grp = tile - grp * group_sz;
+    t.tm = first_m + in_grp % rows_in_group;
+    t.tn = in_grp / rows_in_group;
+    return t;
 }
 
 // a - trunc_tf32(a), exact in f32, plus half a TF32 ulp so that the tensor core's truncation of
@@ -154,21 +176,14 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // Tile of this CTA: m-tiles are visited in groups so that CTAs running together share
-    // B panels (and the A panels of the group) through L2.
-    int64_t tile = blockIdx.x;
-    const int64_t tiles_per_batch = g.tiles_m * g.tiles_n;
-    const int64_t bb = tile / tiles_per_batch;
-    tile -= bb * tiles_per_batch;
-    const int64_t group_sz = (int64_t)g.group_m * g.tiles_n;
-    const int64_t grp = tile / group_sz;
-    const int64_t first_m = grp * g.group_m;
-    const int64_t rows_in_group = min((int64_t)g.group_m, g.tiles_m - first_m);
-    const int64_t in_grp = tile - grp * group_sz;
-    const int64_t tm = first_m + in_grp % rows_in_group;
-    const int64_t tn = in_grp / rows_in_group;
+    // split-K: consecutive CTAs take consecutive k ranges of one tile
+    const int split = (int)(blockIdx.x % (unsigned)g.k_split);
+    const int64_t tile_id = blockIdx.x / (unsigned)g.k_split;
+    const TileCoord tc = decode_tile(tile_id, g.tiles_m, g.tiles_n, g.group_m);
+    const int64_t bb = tc.batch, tm = tc.tm, tn = tc.tn;
     const TileRows tr_m = tile_rows(g.a, tm, kBM, g.M), tr_n = tile_rows(g.b, tn, BN, g.N);
-    const int num_kb = g.num_kb;
+    const int kb_first = split * g.kb_per_split;
+    const int num_kb = min(g.kb_per_split, g.num_kb - kb_first);  // k-blocks of this CTA, numbered from 0 below
     const int num_chunks = (num_kb + kChunk - 1) / kChunk;
 
     if (threadIdx.x == 0) {
@@ -202,7 +217,8 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
                 const uint32_t b_dst = a_dst + Cfg::A_BYTES;
                 mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
-                const int k2 = kb / g.k_blocks1, k1 = (kb - k2 * g.k_blocks1) * kBK;
+                const int kg = kb_first + kb;
+                const int k2 = kg / g.k_blocks1, k1 = (kg - k2 * g.k_blocks1) * kBK;
                 if (g.a.mn_major) {
                     // [32 k][32 m] boxes, one per 32 rows of the tile; with packed tiling every
                     // box finds its own (inner, outer) coordinates from its linear row
@@ -354,7 +370,12 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         while (next_promote < num_chunks) promote(next_promote++);
 
         const int row = lane_grp * 32 + lane;
-        if (row < tr_m.valid) {
+        if (g.k_split > 1) {
+            // raw partial sums, rows fastest; the finishing kernel adds the splits in order
+            float* P = g.partial + ((size_t)(tile_id * g.k_split + split) * BN + col0) * kBM + row;
+#pragma unroll
+            for (int j = 0; j < CPW; ++j) P[(size_t)j * kBM] = acc[j];
+        } else if (row < tr_m.valid) {
             float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
             const int64_t cm = g.c_m[tr_m.base + row];
             const bool read_c = g.beta != 0.f;
@@ -375,6 +396,29 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// Split-K finish: C tile = alpha * (sum of the splits' partial tiles, in split order) + beta * C.
+template <int BN>
+__global__ void __launch_bounds__(256) tf32x3_splitk_finish_kernel(TcArgs g) {
+    const int64_t tile_id = blockIdx.x;
+    const TileCoord tc = decode_tile(tile_id, g.tiles_m, g.tiles_n, g.group_m);
+    const int64_t bb = tc.batch, tm = tc.tm, tn = tc.tn;
+    const TileRows tr_m = tile_rows(g.a, tm, kBM, g.M), tr_n = tile_rows(g.b, tn, BN, g.N);
+    const int row = threadIdx.x & (kBM - 1);
+    if (row >= tr_m.valid) return;
+    float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
+    const int64_t cm = g.c_m[tr_m.base + row];
+    const bool read_c = g.beta != 0.f;
+    const float* P = g.partial + (size_t)tile_id * g.k_split * BN * kBM + row;
+    for (int col = threadIdx.x / kBM; col < tr_n.valid; col += 256 / kBM) {
+        float sum = 0.f;
+        for (int s = 0; s < g.k_split; ++s) sum += P[((size_t)s * BN + col) * kBM];
+        float* p = C + cm + g.c_n[tr_n.base + col];
+        float v = g.alpha * sum;
+        if (read_c) v += g.beta * *p;
+        *p = v;
     }
 }
 
@@ -434,17 +478,11 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
     // Pair tile: 128-row m-tiles 2 tmp, 2 tmp + 1 (one per CTA) x 128-column n-tiles 2 tnp, 2 tnp + 1.
     const int64_t tiles_mp = (g.tiles_m + 1) / 2, tiles_np = (g.tiles_n + 1) / 2;
-    int64_t tile = blockIdx.x >> 1;
-    const int64_t tiles_per_batch = tiles_mp * tiles_np;
-    const int64_t bb = tile / tiles_per_batch;
-    tile -= bb * tiles_per_batch;
-    const int64_t group_sz = (int64_t)g.group_m * tiles_np;
-    const int64_t grp = tile / group_sz;
-    const int64_t first_m = grp * g.group_m;
-    const int64_t rows_in_group = min((int64_t)g.group_m, tiles_mp - first_m);
-    const int64_t in_grp = tile - grp * group_sz;
-    const int64_t tmp = first_m + in_grp % rows_in_group;
-    const int64_t tnp = in_grp / rows_in_group;
+    const unsigned pair_id = blockIdx.x >> 1;
+    const int split = (int)(pair_id % (unsigned)g.k_split);
+    const int64_t pair_tile = pair_id / (unsigned)g.k_split;
+    const TileCoord tc = decode_tile(pair_tile, tiles_mp, tiles_np, g.group_m);
+    const int64_t bb = tc.batch, tmp = tc.tm, tnp = tc.tn;
     // A tile past the end (odd tile counts) has coordinates outside the tensor: TMA fills it
     // with zeros and nothing of it is stored.
     TileRows tr_m = tile_rows(g.a, 2 * tmp + rank, kBM, g.M);
@@ -456,7 +494,8 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         if (2 * tnp + h >= g.tiles_n) tr_n[h].valid = 0;
     }
     const TileRows tr_nl = rank ? tr_n[1] : tr_n[0];  // the half of B this CTA stages
-    const int num_kb = g.num_kb;
+    const int kb_first = split * g.kb_per_split;
+    const int num_kb = min(g.kb_per_split, g.num_kb - kb_first);  // k-blocks of this pair, numbered from 0 below
     const int num_chunks = (num_kb + kChunk - 1) / kChunk;
 
     if (threadIdx.x == 0) {
@@ -490,7 +529,8 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
                 const uint32_t b_dst = a_dst + Cfg::A_BYTES;
                 mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
-                const int k2 = kb / g.k_blocks1, k1 = (kb - k2 * g.k_blocks1) * kBK;
+                const int kg = kb_first + kb;
+                const int k2 = kg / g.k_blocks1, k1 = (kg - k2 * g.k_blocks1) * kBK;
                 if (g.a.mn_major) {
                     for (int c = 0; c < kBM / 32; ++c) {
                         int f1 = tr_m.f1 + 32 * c, f2 = tr_m.f2;
@@ -623,7 +663,12 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
         const int row = lane_grp * 32 + lane;
         const TileRows trn = half ? tr_n[1] : tr_n[0];
-        if (row < tr_m.valid) {
+        if (g.k_split > 1) {
+            // raw partial sums of this CTA's 128 x 256 part, rows fastest
+            float* P = g.partial + ((size_t)((pair_tile * 2 + rank) * g.k_split + split) * BN + col0) * kBM + row;
+#pragma unroll
+            for (int j = 0; j < CPW; ++j) P[(size_t)j * kBM] = acc[j];
+        } else if (row < tr_m.valid) {
             float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
             const int64_t cm = g.c_m[tr_m.base + row];
             const bool read_c = g.beta != 0.f;
@@ -643,6 +688,35 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// Split-K finish for the pair kernel: one CTA per (pair tile, rank), i.e. per 128 x 256 part.
+__global__ void __launch_bounds__(256) tf32x3_pair_splitk_finish_kernel(TcArgs g) {
+    constexpr int BN = PairCfg::BN;
+    const int64_t part = blockIdx.x, pair_tile = part >> 1;
+    const int rank = (int)(part & 1);
+    const int64_t tiles_mp = (g.tiles_m + 1) / 2, tiles_np = (g.tiles_n + 1) / 2;
+    const TileCoord tc = decode_tile(pair_tile, tiles_mp, tiles_np, g.group_m);
+    if (2 * tc.tm + rank >= g.tiles_m) return;
+    const TileRows tr_m = tile_rows(g.a, 2 * tc.tm + rank, kBM, g.M);
+    const int row = threadIdx.x & (kBM - 1);
+    if (row >= tr_m.valid) return;
+    float* C = reinterpret_cast<float*>(g.c) + g.c_b[tc.batch];
+    const int64_t cm = g.c_m[tr_m.base + row];
+    const bool read_c = g.beta != 0.f;
+    const float* P = g.partial + (size_t)part * g.k_split * BN * kBM + row;
+    for (int h = 0; h < 2; ++h) {
+        if (2 * tc.tn + h >= g.tiles_n) break;
+        const TileRows trn = tile_rows(g.b, 2 * tc.tn + h, 128, g.N);
+        for (int j = threadIdx.x / kBM; j < trn.valid; j += 256 / kBM) {
+            float sum = 0.f;
+            for (int s = 0; s < g.k_split; ++s) sum += P[((size_t)s * BN + h * 128 + j) * kBM];
+            float* p = C + cm + g.c_n[trn.base + j];
+            float v = g.alpha * sum;
+            if (read_c) v += g.beta * *p;
+            *p = v;
+        }
     }
 }
 
@@ -747,6 +821,36 @@ OperandMap make_operand_map(const ContractProblem& p, const std::vector<Mode>& f
     return out;
 }
 
+// Split K when the tiles alone leave SMs idle: pick the split that minimises
+// (waves of CTAs) x (k-blocks per CTA + a fixed cost for prologue, epilogue and the finishing
+// pass), preferring fewer splits unless more of them save a tenth.  `slots` = tiles that run at once.
+void choose_k_split(TcArgs* g, int64_t n_tiles, int64_t slots) {
+    g->k_split = 1;
+    g->kb_per_split = g->num_kb;
+    const int want = env_int("TFB_TC_KSPLIT", 0);
+    auto cost = [&](int ksp, int* per) {
+        const int kbp = (g->num_kb + ksp - 1) / ksp, real = (g->num_kb + kbp - 1) / kbp;
+        *per = kbp;
+        return (double)((n_tiles * real + slots - 1) / slots) * (kbp + 8.0) + (real > 1 ? 4.0 : 0.0);
+    };
+    int best = 1, per = g->num_kb;
+    double best_cost = cost(1, &per);
+    if (want > 1) {
+        best = std::min(want, std::max(1, g->num_kb / kChunk));
+    } else if (want == 0) {
+        const int max_split = std::min(64, g->num_kb / kChunk);
+        for (int ksp = 2; ksp <= max_split; ++ksp) {
+            const double c = cost(ksp, &per);
+            if (c < 0.9 * best_cost) { best = ksp; best_cost = c; }
+        }
+    }
+    if (best > 1) {
+        cost(best, &per);
+        g->kb_per_split = per;
+        g->k_split = (g->num_kb + per - 1) / per;
+    }
+}
+
 template <int BN>
 tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcArgs g) {
     using Cfg = TcCfg<BN>;
@@ -771,11 +875,25 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     g.group_m = env_int("TFB_TC_GROUP_M", 16);
     g.elect = env_int("TFB_TC_ELECT", 1);
     g.raw_big = env_int("TFB_TC_RAWBIG", 1);
-    const int64_t grid = g.tiles_m * g.tiles_n * g.B;
+    const int64_t n_tiles = g.tiles_m * g.tiles_n * g.B;
+    choose_k_split(&g, n_tiles, ctx->sm_count);
+    const int64_t grid = n_tiles * g.k_split;
     if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
-    LaunchScope ls(ctx, "contract_tf32x3");
-    contract_tf32x3_kernel<BN><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
-    TFB_CUDA(cudaGetLastError());
+    PoolBlock ws;
+    if (g.k_split > 1) {
+        TFB_TRY(ws.alloc(ctx, (size_t)grid * BN * kBM * sizeof(float)));
+        g.partial = (float*)ws.ptr;
+    }
+    {
+        LaunchScope ls(ctx, "contract_tf32x3");
+        contract_tf32x3_kernel<BN><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+        TFB_CUDA(cudaGetLastError());
+    }
+    if (g.k_split > 1) {
+        LaunchScope ls(ctx, "contract_tf32x3_finish");
+        tf32x3_splitk_finish_kernel<BN><<<(unsigned)n_tiles, 256, 0, ctx->stream>>>(g);
+        TFB_CUDA(cudaGetLastError());
+    }
     return TFB_OK;
 }
 
@@ -802,12 +920,26 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     g.group_m = env_int("TFB_TC_GROUP_M", 8);
     g.elect = 1;
     g.raw_big = 1;
-    const int64_t grid = 2 * ((g.tiles_m + 1) / 2) * ((g.tiles_n + 1) / 2) * g.B;
+    const int64_t pair_tiles = ((g.tiles_m + 1) / 2) * ((g.tiles_n + 1) / 2) * g.B;
+    choose_k_split(&g, pair_tiles, ctx->sm_count / 2);
+    const int64_t grid = 2 * pair_tiles * g.k_split;
     if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
-    LaunchScope ls(ctx, "contract_tf32x3");
-    // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
-    contract_tf32x3_pair_kernel<<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
-    TFB_CUDA(cudaGetLastError());
+    PoolBlock ws;
+    if (g.k_split > 1) {
+        TFB_TRY(ws.alloc(ctx, (size_t)grid * Cfg::BN * kBM * sizeof(float)));
+        g.partial = (float*)ws.ptr;
+    }
+    {
+        LaunchScope ls(ctx, "contract_tf32x3");
+        // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
+        contract_tf32x3_pair_kernel<<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+        TFB_CUDA(cudaGetLastError());
+    }
+    if (g.k_split > 1) {
+        LaunchScope ls(ctx, "contract_tf32x3_finish");
+        tf32x3_pair_splitk_finish_kernel<<<(unsigned)(2 * pair_tiles), 256, 0, ctx->stream>>>(g);
+        TFB_CUDA(cudaGetLastError());
+    }
     return TFB_OK;
 }
 
@@ -883,7 +1015,10 @@ extern "C" tfb_status tfb_probe_tf32_tflops(tfb_ctx* ctx, double* tflops) {
     return TFB_OK;
 }
 
-tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
+// `c_tables`, when given, are device offset tables {batch, row, column} (in floats) that replace
+// the ones derived from p's output strides: the complex path writes into a complex tensor
+// through its f32 view this way.
+tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined, const int64_t* const* c_tables) {
     *declined = true;
     if (p.dtype != TFB_F32) return TFB_OK;
     if (env_int("TFB_NO_TCGEN05", 0)) return TFB_OK;
@@ -893,16 +1028,20 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     if (M > INT32_MAX - 256 || N > INT32_MAX - 256 || K > INT32_MAX - 64) return TFB_OK;
     const int bn = (N >= 256 && env_int("TFB_TC_BN", 256) == 256) ? 256 : 128;
     // Pairs of CTAs on 256 x 256 tiles when the output has room for them.
-    const bool pair = bn == 256 && M >= 256 && env_int("TFB_TC_PAIR", 1);
+    const bool pair = bn == 256 && M > kBM && env_int("TFB_TC_PAIR", 1);
     OperandMap a = make_operand_map(p, p.m, 0, p.a, kBM);
     OperandMap b = make_operand_map(p, p.n, 1, p.b, pair ? 128 : bn);
     if (!a.ok || !b.ok) return TFB_OK;
     std::shared_ptr<ContractTables> t;
-    TFB_TRY(get_tables(ctx, p, &t));
     TcArgs g;
     memset(&g, 0, sizeof g);
     g.c = (char*)p.c;
-    g.c_b = t->c_b; g.c_m = t->c_m; g.c_n = t->c_n;
+    if (c_tables) {
+        g.c_b = c_tables[0]; g.c_m = c_tables[1]; g.c_n = c_tables[2];
+    } else {
+        TFB_TRY(get_tables(ctx, p, &t));
+        g.c_b = t->c_b; g.c_m = t->c_m; g.c_n = t->c_n;
+    }
     g.M = M; g.N = N; g.K = K; g.B = p.B();
     g.alpha = (float)p.alpha.re;
     g.beta = (float)p.beta.re;

@@ -494,6 +494,41 @@ tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t
         return TFB_OK;
     };
 
+    // Label order of the intermediate of step s.  Default: the tree's order.  For Complex32 the
+    // labels its consumer will contract go first, in the memory order of the consumer's other
+    // operand: the consumer then finds the intermediate with unit stride along K and can feed it
+    // to the tensor cores in place instead of copying it (contract_c32.cu).  Only when the
+    // leading label is long enough for the producer's writes to stay coalesced.
+    auto temp_order = [&](size_t s) -> std::vector<uint32_t> {
+        const std::vector<uint32_t>& labs = tree->steps[s].labels;
+        if (dtype != TFB_C32) return labs;
+        const size_t id = n + s;
+        for (size_t c = s + 1; c < tree->steps.size(); ++c) {
+            const TreeStep& cs = tree->steps[c];
+            if (cs.lhs != id && cs.rhs != id) continue;
+            const size_t partner = cs.lhs == id ? cs.rhs : cs.lhs;
+            const std::vector<uint32_t>& kept = (c + 1 == tree->steps.size()) ? out_labels : cs.labels;
+            std::vector<std::pair<int64_t, uint32_t>> by_stride;
+            if (live.count(partner)) {
+                const Live& pl = live[partner];
+                for (size_t d = 0; d < pl.labels.size(); ++d) by_stride.push_back({std::llabs(pl.view.strides[d]), pl.labels[d]});
+            } else if (partner >= n) {
+                const auto& pls = tree->steps[partner - n].labels;
+                for (size_t d = 0; d < pls.size(); ++d) by_stride.push_back({(int64_t)d, pls[d]});
+            }
+            std::stable_sort(by_stride.begin(), by_stride.end(),
+                             [](const auto& x, const auto& y) { return x.first < y.first; });
+            std::vector<uint32_t> order;
+            for (const auto& sl : by_stride)
+                if (has(labs, sl.second) && !has(kept, sl.second) && !has(order, sl.second)) order.push_back(sl.second);
+            if (order.empty() || tree->extent.at(order[0]) < 32) return labs;
+            for (auto lab : labs)
+                if (!has(order, lab)) order.push_back(lab);
+            return order;
+        }
+        return labs;
+    };
+
     size_t next_id = n;
     for (size_t s = 0; s < tree->steps.size(); ++s) {
         const TreeStep& st = tree->steps[s];
@@ -507,7 +542,7 @@ tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t
             TFB_TRY(run_binary(ctx, dtype, x.labels, x.view, y.labels, y.view, out_labels, vout, a, b, 0, &used));
         } else {
             Live t;
-            TFB_TRY(make_temp(st.labels, &t));
+            TFB_TRY(make_temp(temp_order(s), &t));
             TFB_TRY(run_binary(ctx, dtype, x.labels, x.view, y.labels, y.view, t.labels, t.view, one, zero, 0, &used));
             live[next_id] = t;
         }

@@ -60,6 +60,39 @@ def test_tf32x3_alpha_beta_and_batch(tb, oracle):
     assert oracle.rel_frobenius(got, oracle.np_batched_gemm(a, b, 0.5, -2.0, c0)) <= 1e-5
 
 
+@pytest.mark.parametrize("shape", [(384, 640, 96), (300, 700, 200), (256, 256, 8), (1280, 260, 520)])
+@pytest.mark.parametrize("la,lb", [("col", "col"), ("row", "col"), ("col", "row")])
+def test_cta_pair_tiles_odd_counts_and_ragged_edges(tb, oracle, shape, la, lb):
+    """Outputs of 256 x 256 and more run on CTA pairs (two 128-row tiles x two 128-column tiles
+    per pair): odd tile counts leave one CTA of the last pair without a tile, ragged extents
+    leave partial tiles; alpha and beta apply once."""
+    m, n, k = shape
+    rng = np.random.default_rng(11 * m + 5 * n + k)
+    a, b = random_array(rng, (m, k), np.float32), random_array(rng, (k, n), np.float32)
+    c0 = random_array(rng, (m, n), np.float32)
+    got, name = run(tb, a, b, la, lb, tb.ContractKernel.Auto, -1.5, 0.25, c0)
+    assert name == "tcgen05_tf32x3"
+    assert oracle.rel_frobenius(got, oracle.np_batched_gemm(a, b, -1.5, 0.25, c0)) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(96, 96, 9216), (96, 1000, 4096), (200, 120, 2052), (2, 130, 300, 1536)])
+def test_split_k_for_small_outputs_with_long_k(tb, oracle, shape):
+    """Few output tiles and a long K: the k-blocks of a tile are shared out among several CTAs
+    and a finishing kernel adds their partial tiles in a fixed order (so reruns agree bit for
+    bit) and applies alpha and beta."""
+    *batch, m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a, b = random_array(rng, (*batch, m, k), np.float32), random_array(rng, (*batch, k, n), np.float32)
+    c0 = random_array(rng, (*batch, m, n), np.float32)
+    want = oracle.np_batched_gemm(a, b, 2.0, -0.5, c0)
+    lb = "row" if batch else "col"  # column-major with a batch puts the unit stride on the batch mode
+    got, name = run(tb, a, b, "row", lb, tb.ContractKernel.Auto, 2.0, -0.5, c0)
+    assert name == "tcgen05_tf32x3"
+    assert oracle.rel_frobenius(got, want) <= 1e-5
+    again, _ = run(tb, a, b, "row", lb, tb.ContractKernel.Auto, 2.0, -0.5, c0)
+    assert np.array_equal(got, again)
+
+
 def test_layouts_tma_cannot_describe_fall_back(tb, oracle):
     rng = np.random.default_rng(5)
     a, b = random_array(rng, (130, 67), np.float32), random_array(rng, (67, 150), np.float32)
@@ -119,9 +152,10 @@ def test_tf32x3_two_modes_per_group(tb, oracle, case):
 
 
 @pytest.mark.parametrize("shape", [(64, 96, 40), (130, 70, 33), (256, 256, 512), (96, 1152, 96)])
-def test_complex64_three_products_on_tensor_cores(tb, oracle, shape):
-    """Complex32 contractions: planes gathered from any layout (conj folded in), three real
-    3xTF32 products, complex alpha/beta on the way out."""
+def test_complex64_on_tensor_cores(tb, oracle, shape):
+    """Complex32 contractions as one real product of doubled extents: the 2 x 2 real embedding of
+    A gathered from any layout (conj and alpha folded in), B copied K-major or used in place,
+    the result written straight into the complex output; complex beta applied beforehand."""
     m, n, k = shape
     rng = np.random.default_rng(m + n + k)
     for trial, layout in enumerate(("col", "row", "random")):
