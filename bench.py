@@ -410,7 +410,10 @@ def wl_dense(env: Env):
         mode = f"contracted pair (k,l) split {W} ways on l, partial outputs reduce-scattered over NCCL"
         result_t, keep = out_t, (a_t, b_t, part_t, out_t)
     flops = 2.0 * i * j * m * n * k * l
-    tf32 = ctx.probe_tf32_tflops
+    # The probe runs once before the workload (cool GPU) and once after (under the power cap the
+    # clock has dropped by then); the larger figure is the denominator.
+    tf32_cold = ctx.probe_tf32_tflops()
+    tf32 = lambda: max(tf32_cold, ctx.probe_tf32_tflops())
 
     def read_result():
         ctx.synchronize()
@@ -419,10 +422,12 @@ def wl_dense(env: Env):
     return {
         "metric": "einsum GFLOP/s ('ijkl,klmn->ijmn', f32 via 3xTF32)", "unit": "GFLOP/s", "dtype": "f32 (3xTF32)",
         "scaling": "strong", "step": step, "work": flops, "read_result": read_result, "e2e_step": None, "h2d": 0, "d2h": 0,
-        "kernel": "contract_tf32x3", "kernel_label": "contract_tf32x3_kernel (tcgen05, 128x256x32 tiles)",
+        "kernel": "contract_tf32x3",
+        "kernel_label": "contract_tf32x3_pair_kernel (tcgen05 cta_group::2, 256x256 tiles per CTA pair, 32-deep stages)",
         "per_launch": flops / W, "bound": "tensor", "peak": lambda: tf32() / 3.0,
         "peak_source": "one third of the dense TF32 rate measured on this GPU by the library's tcgen05 probe (three "
-                       "MMAs per algorithmic MMA); MEASURED_PEAKS.json holds no TF32 figure",
+                       "MMAs per algorithmic MMA), the larger of a probe before and one after the run; MEASURED_PEAKS.json "
+                       "holds no TF32 figure",
         "extra_kernels": [], "keep": keep,
         "config": {"workload": f"'{notation}' f32, i=j=m=n={i}, k=l={k}, N(0,1)", "parallelism": mode,
                    "l2": f"inputs larger than L2: A and B hold {(a_t.numel() + b_t.numel()) * 4 >> 20} MiB",
@@ -499,6 +504,7 @@ def wl_network4(env: Env):
     tree = tb.ContractionTree.optimize(tb.Subscripts.parse(notation), [a.shape for a in arrays])
     call = tb.PreparedEinsum(tree, ops, out)
     flops = 8.0 * tree.macs
+    tf32_cold = ctx.probe_tf32_tflops()
 
     def read_result():
         return out.to_numpy()
@@ -506,9 +512,12 @@ def wl_network4(env: Env):
     return {
         "metric": "einsum GFLOP/s ('ijk,jlm,kmn,lnp->ip', complex64)", "unit": "GFLOP/s", "dtype": "c64 (f32 arithmetic)",
         "scaling": "weak", "step": call.run, "work": flops * env.world, "read_result": read_result, "e2e_step": None,
-        "h2d": 0, "d2h": 0, "kernel": "contract_simt", "kernel_label": "contract_simt_kernel (complex64 FMA)",
-        "per_launch": flops / 3.0, "bound": "tensor", "peak": lambda: ctx.probe_tf32_tflops() / 3.0,
-        "peak_source": "one third of the library's dense TF32 probe", "extra_kernels": [],
+        "h2d": 0, "d2h": 0, "kernel": "contract_tf32x3",
+        "kernel_label": "contract_tf32x3 kernels (tcgen05; complex64 as one real product of doubled extents per tree node)",
+        "per_launch": flops / 3.0, "bound": "tensor", "peak": lambda: max(tf32_cold, ctx.probe_tf32_tflops()) / 3.0,
+        "peak_source": "one third of the library's dense TF32 probe: a complex multiply-add (8 flop) costs four real "
+                       "ones, each three TF32 MMAs (24 TF32 flop)",
+        "extra_kernels": ["pack_planes", "contract_tf32x3_finish"],
         "config": {"workload": f"'{notation}' complex64, every index {dim}, N(0,1) parts; tree {tree.pairs}",
                    "parallelism": f"{env.world} independent replica(s)",
                    "l2": f"intermediates of {dim ** 4 * 8 >> 20} MiB exceed L2" if dim >= 64 else "L2-resident (scaled down)",
