@@ -720,6 +720,45 @@ __global__ void __launch_bounds__(256) tf32x3_pair_splitk_finish_kernel(TcArgs g
     }
 }
 
+// ------------------------------------------------------------------ operand repack
+// Copies one operand, through its offset tables, into a K-major block [batch][row][Kp].  Used
+// for large products whose operand TMA cannot describe, or could only tile with mostly
+// padding (a free index left with a short extent by sharding): one extra pass over that
+// operand is noise next to the product, the exact-FMA fallback is not.
+struct RepackArgs {
+    const float* src;
+    const int64_t* row_tab;
+    const int64_t* k_tab;
+    const int64_t* b_tab;
+    int64_t rows, K, Kp, B;
+    int src_kfast;
+    float* dst;
+};
+__global__ void __launch_bounds__(256) repack_kmajor_kernel(RepackArgs g) {
+    __shared__ float tile[32][33];
+    const int64_t tiles_r = (g.rows + 31) / 32, tiles_k = (g.Kp + 31) / 32;
+    const int64_t n_tiles = tiles_r * tiles_k * g.B;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int64_t tr = t % tiles_r, rest = t / tiles_r, tk = rest % tiles_k, b = rest / tiles_k;
+        const int64_t r0 = tr * 32, k0 = tk * 32;
+        const float* src = g.src + g.b_tab[b];
+        for (int j = ty; j < 32; j += 8) {
+            // tx runs along the source's fast direction
+            const int64_t r = r0 + (g.src_kfast ? j : tx), k = k0 + (g.src_kfast ? tx : j);
+            float v = 0.f;
+            if (r < g.rows && k < g.K) v = src[g.row_tab[r] + g.k_tab[k]];
+            if (g.src_kfast) tile[j][tx] = v; else tile[tx][j] = v;  // tile[r][k]
+        }
+        __syncthreads();
+        for (int j = ty; j < 32; j += 8) {
+            const int64_t r = r0 + j, k = k0 + tx;
+            if (r < g.rows && k < g.Kp) g.dst[(b * g.rows + r) * g.Kp + k] = tile[j][tx];
+        }
+        __syncthreads();
+    }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1029,17 +1068,58 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     const int bn = (N >= 256 && env_int("TFB_TC_BN", 256) == 256) ? 256 : 128;
     // Pairs of CTAs on 256 x 256 tiles when the output has room for them.
     const bool pair = bn == 256 && M > kBM && env_int("TFB_TC_PAIR", 1);
+    const int rows_b = pair ? 128 : bn;
     OperandMap a = make_operand_map(p, p.m, 0, p.a, kBM);
-    OperandMap b = make_operand_map(p, p.n, 1, p.b, pair ? 128 : bn);
-    if (!a.ok || !b.ok) return TFB_OK;
+    OperandMap b = make_operand_map(p, p.n, 1, p.b, rows_b);
     std::shared_ptr<ContractTables> t;
+    PoolBlock packed_a, packed_b;
+    // Large products only: repack an operand that has no tensor map, or whose tiles would be
+    // more than a third padding.
+    if (!c_tables && 2.0 * M * N * K >= 1e9 && p.batch.size() <= 1 && p.k.size() <= 2) {
+        auto wasteful = [](const OperandMap& o, int64_t total, int rows) {
+            if (!o.ok) return true;
+            if (o.geom.pack) return false;
+            return (total / o.geom.e1) * o.geom.tiles1 * rows > total + total / 2;
+        };
+        const bool pack_a = wasteful(a, M, kBM), pack_b = wasteful(b, N, rows_b);
+        if (pack_a || pack_b) {
+            TFB_TRY(get_tables(ctx, p, &t));
+            ContractArgs ca;
+            fill_args(p, *t, &ca);
+            const int64_t Kp = (K + 3) / 4 * 4, Bn = p.B();
+            auto repack = [&](int tns, PoolBlock* blk, OperandMap* out) -> tfb_status {
+                const int64_t rows = tns == 0 ? M : N;
+                TFB_TRY(blk->alloc(ctx, (size_t)(rows * Kp * Bn) * sizeof(float)));
+                RepackArgs r{(const float*)(tns == 0 ? p.a : p.b), tns == 0 ? t->a_m : t->b_n, tns == 0 ? t->a_k : t->b_k,
+                             tns == 0 ? t->a_b : t->b_b, rows, K, Kp, Bn, tns == 0 ? ca.a_kfast : ca.b_kfast, (float*)blk->ptr};
+                const int64_t n_tiles = ((rows + 31) / 32) * ((Kp + 31) / 32) * Bn;
+                {
+                    LaunchScope ls(ctx, "repack_operand");
+                    repack_kmajor_kernel<<<(unsigned)std::min<int64_t>(n_tiles, (int64_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>(r);
+                    TFB_CUDA(cudaGetLastError());
+                }
+                // the same product with this operand contiguous: one free mode, K split as in the other operand
+                ContractProblem q = p;
+                std::vector<Mode> free_q{Mode{rows, {0, 0, 0}}};
+                free_q[0].s[tns] = Kp;
+                int64_t run = 1;
+                for (Mode& m : q.k) { m.s[tns] = run; run *= m.extent; }
+                for (Mode& m : q.batch) m.s[tns] = rows * Kp;
+                *out = make_operand_map(q, free_q, tns, blk->ptr, tns == 0 ? kBM : rows_b);
+                return TFB_OK;
+            };
+            if (pack_a) TFB_TRY(repack(0, &packed_a, &a));
+            if (pack_b) TFB_TRY(repack(1, &packed_b, &b));
+        }
+    }
+    if (!a.ok || !b.ok) return TFB_OK;
     TcArgs g;
     memset(&g, 0, sizeof g);
     g.c = (char*)p.c;
     if (c_tables) {
         g.c_b = c_tables[0]; g.c_m = c_tables[1]; g.c_n = c_tables[2];
     } else {
-        TFB_TRY(get_tables(ctx, p, &t));
+        if (!t) TFB_TRY(get_tables(ctx, p, &t));
         g.c_b = t->c_b; g.c_m = t->c_m; g.c_n = t->c_n;
     }
     g.M = M; g.N = N; g.K = K; g.B = p.B();

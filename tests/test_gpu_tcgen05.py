@@ -124,6 +124,10 @@ def test_einsum_ijkl_klmn_uses_tensor_cores(tb, oracle):
 @pytest.mark.parametrize("case", [
     # (labels_a, shape_a, labels_b, shape_b, labels_c): groups with two non-fusable modes each way
     ("free pair, MN-major, packed", [0, 1, 2], (64, 6, 40), [2, 3], (40, 72), [0, 1, 3], "sub_i"),
+    ("free pair, MN-major, inner extent 16 (what sharding a mode eight ways leaves): tiles mostly padding",
+     [0, 1, 2], (32, 40, 48), [2, 3], (48, 264), [0, 1, 3], "sub_i"),
+    ("the same at a size where the operand is repacked K-major first", [0, 1, 2], (32, 256, 512), [2, 3], (512, 512),
+     [0, 1, 3], "sub_i"),
     ("free pair, K-major, inner extent 96 padded to the tile", [2, 0, 1], (64, 96, 5), [2, 3], (64, 160), [0, 1, 3], None),
     ("free pair, K-major, packed small inner extent", [2, 0, 1], (48, 32, 9), [2, 3], (48, 96), [0, 1, 3], None),
     ("contracted pair not fusable in B", [0, 1, 2], (96, 96, 40), [3, 2, 1, 4], (24, 40, 96, 3), [0, 3, 4], None),
