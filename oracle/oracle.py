@@ -253,7 +253,11 @@ def np_einsum(notation_or_labels, operands: Sequence[np.ndarray], alpha=1.0, bet
     args = []
     for op, labels in zip(operands, ins):
         args += [np.asarray(op).astype(w), list(labels)]
-    val = np.einsum(*args, uniq, optimize=True)
+    simple = len(operands) >= 3 and len(uniq) == len(out) and all(len(set(l)) == len(l) for l in ins)
+    if simple:
+        val = _pairwise(ins, [np.asarray(op).astype(w) for op in operands], uniq)
+    else:
+        val = np.einsum(*args, uniq, optimize=True)
     if len(uniq) != len(out):
         ext = {l: val.shape[i] for i, l in enumerate(uniq)}
         full = np.zeros([ext[l] for l in out], dtype=w)
@@ -261,6 +265,46 @@ def np_einsum(notation_or_labels, operands: Sequence[np.ndarray], alpha=1.0, bet
             full[tuple(idx[uniq.index(l)] for l in out)] = val[idx]
         val = full
     return _finish(val, alpha, beta, out_old, dtype)
+
+
+def _pairwise(ins, ops, out):
+    """N-ary contraction as a greedy sequence of pairwise permute + GEMM steps (smallest
+    intermediate first).  numpy's own einsum leaves BLAS for some complex networks and then
+    needs minutes where this needs milliseconds; same sums, different order."""
+    ins, ops = [list(l) for l in ins], list(ops)
+    while len(ops) > 1:
+        best = None
+        for x in range(len(ops)):
+            for y in range(x + 1, len(ops)):
+                others = set(out)
+                for z in range(len(ops)):
+                    if z != x and z != y:
+                        others |= set(ins[z])
+                keep = [l for l in dict.fromkeys(ins[x] + ins[y]) if l in others]
+                ext = {l: ops[x].shape[i] for i, l in enumerate(ins[x])}
+                ext.update({l: ops[y].shape[i] for i, l in enumerate(ins[y])})
+                size = int(np.prod([ext[l] for l in keep], dtype=np.int64)) if keep else 1
+                shared = bool(set(ins[x]) & set(ins[y]))
+                key = (not shared, size)
+                if best is None or key < best[0]:
+                    best = (key, x, y, keep)
+        _, x, y, keep = best
+        only_x = [l for l in ins[x] if l not in keep and l not in ins[y]]
+        only_y = [l for l in ins[y] if l not in keep and l not in ins[x]]
+        a, la = ops[x], ins[x]
+        b, lb = ops[y], ins[y]
+        if only_x:
+            a = a.sum(axis=tuple(la.index(l) for l in only_x))
+            la = [l for l in la if l not in only_x]
+        if only_y:
+            b = b.sum(axis=tuple(lb.index(l) for l in only_y))
+            lb = [l for l in lb if l not in only_y]
+        val = ttgt_contract(la, a, lb, b, keep)
+        for z in sorted((x, y), reverse=True):
+            del ops[z], ins[z]
+        ops.append(val)
+        ins.append(keep)
+    return np.transpose(ops[0], [ins[0].index(l) for l in out])
 
 
 def tree_macs(inputs: Sequence[Sequence[int]], output: Sequence[int], extents: Dict[int, int],
