@@ -145,9 +145,9 @@ __global__ void __launch_bounds__(256) permute_tiled_kernel(LoopNest nest, const
 
 // Vector variant of the tiled transpose for 4- and 8-byte elements: 16-byte loads along the
 // input's unit stride, 16-byte stores along the output's, every load of a thread issued before
-// the first use (16 KB in flight per CTA).  Needs both sides 16-byte aligned.
-template <typename T, int V>
-__global__ void __launch_bounds__(256) permute_tiled_vec_kernel(LoopNest nest, const T* __restrict__ in, T* out,
+// the first use (16 KB in flight per CTA; MINB CTAs per SM).  Needs both sides 16-byte aligned.
+template <typename T, int V, int MINB>
+__global__ void __launch_bounds__(256, MINB) permute_tiled_vec_kernel(LoopNest nest, const T* __restrict__ in, T* out,
                                                                 EpilogueArgs<T> ep, int64_t tiles_i, int64_t tiles_j,
                                                                 int64_t n_tiles) {
     constexpr int TILE = 64, VPR = TILE / V, LOADS = TILE * TILE / V / 256;
@@ -261,8 +261,12 @@ static tfb_status permute_typed(tfb_ctx* ctx, const LoopNest& nest_out_order, co
                 tj = (r.extent[1] + 63) / 64;
                 n_tiles = ti * tj * rest;
                 grid = (int)(n_tiles < cap ? n_tiles : cap);
-                permute_tiled_vec_kernel<T, (V > 1 ? V : 2)><<<grid, 256, 0, ctx->stream>>>(r, (const T*)in, (T*)out, ep, ti,
-                                                                                            tj, n_tiles);
+                // CTAs per SM: each holds 16 KB of loads in flight, and HBM wants about 90 KB per SM.
+                // Six fit for 4-byte elements (40 registers); the 33 KB tiles of 8-byte elements do
+                // best at three.
+                constexpr int kOcc = sizeof(T) == 4 ? 6 : 3;
+                permute_tiled_vec_kernel<T, (V > 1 ? V : 2), kOcc><<<grid, 256, 0, ctx->stream>>>(r, (const T*)in, (T*)out, ep,
+                                                                                                  ti, tj, n_tiles);
                 TFB_CUDA(cudaGetLastError());
                 return TFB_OK;
             }
