@@ -437,9 +437,9 @@ __global__ void __launch_bounds__(256) tf32x3_splitk_finish_kernel(TcArgs g) {
 //   empty[s]     each CTA  MMAs that read stage s retired (commit to both) -> own producer
 //   chunk[b]     each CTA  work accumulator b complete (commit to both)    -> own converters
 //   promoted[b]  LEADER    both CTAs have read work accumulator b          -> MMA thread
-// Arrivals on the leader's barriers from the other CTA are cluster-scope releases on the mapped
-// address; commits go to each CTA's barrier by its own instruction, so no instruction here
-// is a multicast.
+// Arrivals on the leader's barriers from the other CTA go to the mapped address with CTA-scope
+// release semantics (see mbar_arrive_cluster); commits go to each CTA's barrier by an
+// instruction of its own, so every instruction here addresses exactly one CTA.
 struct PairCfg {
     static constexpr int BN = 256;                  // tile columns of the pair
     static constexpr int A_BYTES = kBM * kBK * 4;   // 16 KB: this CTA's 128 rows
