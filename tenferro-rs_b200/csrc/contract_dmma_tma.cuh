@@ -237,8 +237,12 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         } else {
             if (ke < g.k_iters) {
                 const int64_t g_last = ((tile + 1) * g.k_iters - 1) / g.iters_per_cta;
-                for (int64_t c = (int64_t)blockIdx.x + 1; c <= g_last; ++c) {
-                    if (tid == 0) {
+                // All contributors' flags first (thread c - first polls flag c, bounded), then one
+                // pass over their slots in CTA order: the loads of different slots overlap, the
+                // additions keep their order, so the sum does not depend on timing.
+                {
+                    const int64_t c = (int64_t)blockIdx.x + 1 + tid;
+                    if (c <= g_last) {
                         uint32_t v = 0;
                         for (uint32_t spin = 0; spin < (1u << 20); ++spin) {
                             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(g.sk_flags + c) : "memory");
@@ -248,6 +252,9 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         if (v != g.sk_epoch) atomicCAS(status, 0, 0x303);
                     }
                     __syncthreads();
+                }
+#pragma unroll 4
+                for (int64_t c = (int64_t)blockIdx.x + 1; c <= g_last; ++c) {
                     const char* P = g.partial + (size_t)c * (BM * BN) * ES;
 #pragma unroll
                     for (int i = 0; i < TM; ++i)
@@ -397,9 +404,9 @@ static tfb_status run_tma_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractAr
     } else {
         grid = std::min<int64_t>(slots, std::max<int64_t>(1, a.total_iters / 4));
         a.iters_per_cta = (a.total_iters + grid - 1) / grid;
-        // The owner of a tile adds the other ranges' accumulators one after the other: keep a
-        // tile in at most 16 pieces.
-        a.iters_per_cta = std::max<int64_t>(a.iters_per_cta, (a.k_iters + 15) / 16);
+        // One thread of the owner polls each contributor's flag and every contribution costs the
+        // owner one pass over a slot: keep a tile in at most 32 pieces.
+        a.iters_per_cta = std::max<int64_t>(a.iters_per_cta, (a.k_iters + 31) / 32);
     }
     grid = (a.total_iters + a.iters_per_cta - 1) / a.iters_per_cta;
     const bool cuts = a.iters_per_cta % a.k_iters != 0;
