@@ -400,6 +400,7 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 }
 
 // Split-K finish: C tile = alpha * (sum of the splits' partial tiles, in split order) + beta * C.
+constexpr int kFinishCols = 8;  // columns of a tile per finishing CTA
 template <int BN>
 __global__ void __launch_bounds__(256) tf32x3_splitk_finish_kernel(TcArgs g) {
     const int64_t tile_id = blockIdx.x;
@@ -412,8 +413,11 @@ __global__ void __launch_bounds__(256) tf32x3_splitk_finish_kernel(TcArgs g) {
     const int64_t cm = g.c_m[tr_m.base + row];
     const bool read_c = g.beta != 0.f;
     const float* P = g.partial + (size_t)tile_id * g.k_split * BN * kBM + row;
-    for (int col = threadIdx.x / kBM; col < tr_n.valid; col += 256 / kBM) {
+    // blockIdx.y takes kFinishCols columns of the tile; two columns are in flight per pass
+    const int col_end = min(tr_n.valid, (int)(blockIdx.y + 1) * kFinishCols);
+    for (int col = blockIdx.y * kFinishCols + threadIdx.x / kBM; col < col_end; col += 256 / kBM) {
         float sum = 0.f;
+#pragma unroll 8
         for (int s = 0; s < g.k_split; ++s) sum += P[((size_t)s * BN + col) * kBM];
         float* p = C + cm + g.c_n[tr_n.base + col];
         float v = g.alpha * sum;
@@ -453,6 +457,35 @@ struct PairCfg {
     static_assert(kChunk >= STAGES, "promotion lag assumes a chunk spans at least the ring");
 };
 
+// One unit of work of a CTA pair: a 256 x 256 pair tile (128-row m-tiles 2 tmp, 2 tmp + 1, one per
+// CTA, x 128-column n-tiles 2 tnp, 2 tnp + 1) and, with split-K, one k range of it.
+struct PairWork {
+    int64_t batch, pair_tile;
+    int split, kb_first, num_kb;
+    TileRows tr_m;      // this CTA's rows
+    TileRows tr_n[2];   // the two column halves of the tile
+};
+__device__ __forceinline__ PairWork pair_work(const TcArgs& g, int64_t w, uint32_t rank) {
+    PairWork pw;
+    const int64_t tiles_mp = (g.tiles_m + 1) / 2, tiles_np = (g.tiles_n + 1) / 2;
+    pw.split = (int)(w % g.k_split);
+    pw.pair_tile = w / g.k_split;
+    const TileCoord tc = decode_tile(pw.pair_tile, tiles_mp, tiles_np, g.group_m);
+    pw.batch = tc.batch;
+    // A tile past the end (odd tile counts) has coordinates outside the tensor: TMA fills it
+    // with zeros and nothing of it is stored.
+    pw.tr_m = tile_rows(g.a, 2 * tc.tm + rank, kBM, g.M);
+    if (2 * tc.tm + rank >= g.tiles_m) pw.tr_m.valid = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        pw.tr_n[h] = tile_rows(g.b, 2 * tc.tn + h, 128, g.N);
+        if (2 * tc.tn + h >= g.tiles_n) pw.tr_n[h].valid = 0;
+    }
+    pw.kb_first = pw.split * g.kb_per_split;
+    pw.num_kb = min(g.kb_per_split, g.num_kb - pw.kb_first);
+    return pw;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + kSplitThreads, 1)
 contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
     using Cfg = PairCfg;
@@ -476,27 +509,13 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const uint32_t rank = cluster_ctarank();
     constexpr int kWarps = kSplitThreads / 32;
 
-    // Pair tile: 128-row m-tiles 2 tmp, 2 tmp + 1 (one per CTA) x 128-column n-tiles 2 tnp, 2 tnp + 1.
-    const int64_t tiles_mp = (g.tiles_m + 1) / 2, tiles_np = (g.tiles_n + 1) / 2;
-    const unsigned pair_id = blockIdx.x >> 1;
-    const int split = (int)(pair_id % (unsigned)g.k_split);
-    const int64_t pair_tile = pair_id / (unsigned)g.k_split;
-    const TileCoord tc = decode_tile(pair_tile, tiles_mp, tiles_np, g.group_m);
-    const int64_t bb = tc.batch, tmp = tc.tm, tnp = tc.tn;
-    // A tile past the end (odd tile counts) has coordinates outside the tensor: TMA fills it
-    // with zeros and nothing of it is stored.
-    TileRows tr_m = tile_rows(g.a, 2 * tmp + rank, kBM, g.M);
-    if (2 * tmp + rank >= g.tiles_m) tr_m.valid = 0;
-    TileRows tr_n[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        tr_n[h] = tile_rows(g.b, 2 * tnp + h, 128, g.N);
-        if (2 * tnp + h >= g.tiles_n) tr_n[h].valid = 0;
-    }
-    const TileRows tr_nl = rank ? tr_n[1] : tr_n[0];  // the half of B this CTA stages
-    const int kb_first = split * g.kb_per_split;
-    const int num_kb = min(g.kb_per_split, g.num_kb - kb_first);  // k-blocks of this pair, numbered from 0 below
-    const int num_chunks = (num_kb + kChunk - 1) / kChunk;
+    // Persistent: this pair takes work items w0, w0 + wstep, ...  Every role walks the same
+    // sequence with running counters (k-blocks for the stage ring, chunks for the two work
+    // accumulators), so the producer is already loading the next tile while the converter
+    // warps store the current one, and barriers, tensor memory and the cluster handshake are
+    // set up once per CTA instead of once per tile.
+    const int64_t n_work = ((g.tiles_m + 1) / 2) * ((g.tiles_n + 1) / 2) * g.B * g.k_split;
+    const int64_t w0 = blockIdx.x >> 1, wstep = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -522,14 +541,19 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (each CTA its own tiles)
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t use = kb / STAGES;
+            uint32_t it = 0;
+            for (int64_t w = w0; w < n_work; w += wstep) {
+            const PairWork pw = pair_work(g, w, rank);
+            const TileRows tr_m = pw.tr_m, tr_nl = rank ? pw.tr_n[1] : pw.tr_n[0];  // tr_nl: the half of B this CTA stages
+            const int64_t bb = pw.batch;
+            for (int kb = 0; kb < pw.num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t use = it / STAGES;
                 mbar_wait(bar_empty(s), (use & 1) ^ 1, g.status, 0x111);
                 const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
                 const uint32_t b_dst = a_dst + Cfg::A_BYTES;
                 mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
-                const int kg = kb_first + kb;
+                const int kg = pw.kb_first + kb;
                 const int k2 = kg / g.k_blocks1, k1 = (kg - k2 * g.k_blocks1) * kBK;
                 if (g.a.mn_major) {
                     for (int c = 0; c < kBM / 32; ++c) {
@@ -558,6 +582,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     tma_load_5d(b_dst, &map_b, bar_full(s), k1, k2, tr_nl.f1, tr_nl.f2, (int)bb);
                 }
             }
+            }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer (leader CTA only)
@@ -569,10 +594,15 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t a_sbo = g.a.mn_major ? 512u : 1024u, b_sbo = g.b.mn_major ? 512u : 1024u;
             const uint32_t a_lay = g.a.mn_major ? 1u : 2u, b_lay = g.b.mn_major ? 1u : 2u;
             const uint32_t a_step = g.a.mn_major ? 1024u : 32u, b_step = g.b.mn_major ? 1024u : 32u;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t use = kb / STAGES;
-                const int chunk = kb / kChunk, buf = chunk & 1;
+            uint32_t it = 0, ch0 = 0;  // k-blocks and chunks issued before this work item
+            for (int64_t w = w0; w < n_work; w += wstep) {
+            const PairWork pw = pair_work(g, w, rank);
+            const int num_kb = pw.num_kb;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t use = it / STAGES;
+                const uint32_t chunk = ch0 + kb / kChunk;
+                const int buf = chunk & 1;
                 const bool chunk_first = kb % kChunk == 0;
                 const bool chunk_last = (kb % kChunk == kChunk - 1) || kb == num_kb - 1;
                 if (chunk_first && chunk >= 2) {
@@ -603,6 +633,8 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     tc_commit_pair(map_to_cta(bar_chunk(buf), 1));
                 }
             }
+            ch0 += (uint32_t)((num_kb + kChunk - 1) / kChunk);
+            }
         }
     } else {
         // ---------------------------------------------------------------- split + promote, then epilogue
@@ -613,12 +645,10 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         const uint32_t tmem_mine = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)col0;
         const uint32_t leader_split0 = map_to_cta(bar_split(0), 0), leader_promoted0 = map_to_cta(bar_promoted(0), 0);
         float acc[CPW];
-#pragma unroll
-        for (int j = 0; j < CPW; ++j) acc[j] = 0.f;
-        int next_promote = 0;
-        auto promote = [&](int chunk) {
+        uint32_t it = 0, ch0 = 0;  // k-blocks and chunks handled before this work item
+        auto promote = [&](uint32_t chunk) {
             const int buf = chunk & 1;
-            if (lane == 0) mbar_wait(bar_chunk(buf), (uint32_t)(chunk >> 1) & 1, g.status, 0x114);
+            if (lane == 0) mbar_wait(bar_chunk(buf), (chunk >> 1) & 1, g.status, 0x114);
             __syncwarp();
             tc_fence_after();
 #pragma unroll
@@ -633,9 +663,17 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_promoted0 + 8u * buf);
         };
-        for (int kb = 0; kb < num_kb; ++kb) {
-            const int s = kb % STAGES;
-            const uint32_t use = kb / STAGES;
+        for (int64_t w = w0; w < n_work; w += wstep) {
+        const PairWork pw = pair_work(g, w, rank);
+        const int num_kb = pw.num_kb, num_chunks = (num_kb + kChunk - 1) / kChunk;
+        const TileRows tr_m = pw.tr_m;
+        const int64_t bb = pw.batch;
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) acc[j] = 0.f;
+        int next_promote = 0;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t use = it / STAGES;
             if (lane == 0) mbar_wait(bar_full(s), use & 1, g.status, 0x113);
             __syncwarp();
             char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
@@ -657,15 +695,16 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             if (lane == 0) mbar_arrive_cluster(leader_split0 + 8u * s);
             while (next_promote < num_chunks &&
                    min((next_promote + 1) * kChunk, num_kb) - 1 + STAGES <= kb)
-                promote(next_promote++);
+                promote(ch0 + next_promote++);
         }
-        while (next_promote < num_chunks) promote(next_promote++);
+        while (next_promote < num_chunks) promote(ch0 + next_promote++);
+        ch0 += (uint32_t)num_chunks;
 
         const int row = lane_grp * 32 + lane;
-        const TileRows trn = half ? tr_n[1] : tr_n[0];
+        const TileRows trn = half ? pw.tr_n[1] : pw.tr_n[0];
         if (g.k_split > 1) {
             // raw partial sums of this CTA's 128 x 256 part, rows fastest
-            float* P = g.partial + ((size_t)((pair_tile * 2 + rank) * g.k_split + split) * BN + col0) * kBM + row;
+            float* P = g.partial + ((size_t)((pw.pair_tile * 2 + rank) * g.k_split + pw.split) * BN + col0) * kBM + row;
 #pragma unroll
             for (int j = 0; j < CPW; ++j) P[(size_t)j * kBM] = acc[j];
         } else if (row < tr_m.valid) {
@@ -681,6 +720,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     *p = v;
                 }
             }
+        }
         }
     }
     tc_fence_before();
@@ -706,11 +746,15 @@ __global__ void __launch_bounds__(256) tf32x3_pair_splitk_finish_kernel(TcArgs g
     const int64_t cm = g.c_m[tr_m.base + row];
     const bool read_c = g.beta != 0.f;
     const float* P = g.partial + (size_t)part * g.k_split * BN * kBM + row;
-    for (int h = 0; h < 2; ++h) {
-        if (2 * tc.tn + h >= g.tiles_n) break;
+    // blockIdx.y takes kFinishCols columns of one of the two 128-column halves
+    {
+        const int h = (int)(blockIdx.y * kFinishCols) / 128, j0 = (int)(blockIdx.y * kFinishCols) % 128;
+        if (2 * tc.tn + h >= g.tiles_n) return;
         const TileRows trn = tile_rows(g.b, 2 * tc.tn + h, 128, g.N);
-        for (int j = threadIdx.x / kBM; j < trn.valid; j += 256 / kBM) {
+        const int j_end = min(trn.valid, j0 + kFinishCols);
+        for (int j = j0 + threadIdx.x / kBM; j < j_end; j += 256 / kBM) {
             float sum = 0.f;
+#pragma unroll 8
             for (int s = 0; s < g.k_split; ++s) sum += P[((size_t)s * BN + h * 128 + j) * kBM];
             float* p = C + cm + g.c_n[trn.base + j];
             float v = g.alpha * sum;
@@ -930,7 +974,7 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     }
     if (g.k_split > 1) {
         LaunchScope ls(ctx, "contract_tf32x3_finish");
-        tf32x3_splitk_finish_kernel<BN><<<(unsigned)n_tiles, 256, 0, ctx->stream>>>(g);
+        tf32x3_splitk_finish_kernel<BN><<<dim3((unsigned)n_tiles, BN / kFinishCols), 256, 0, ctx->stream>>>(g);
         TFB_CUDA(cudaGetLastError());
     }
     return TFB_OK;
@@ -961,11 +1005,13 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     g.raw_big = 1;
     const int64_t pair_tiles = ((g.tiles_m + 1) / 2) * ((g.tiles_n + 1) / 2) * g.B;
     choose_k_split(&g, pair_tiles, ctx->sm_count / 2);
-    const int64_t grid = 2 * pair_tiles * g.k_split;
-    if (grid > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
+    const int64_t n_work = pair_tiles * g.k_split;
+    if (2 * n_work > 0x7fffffff) return fail(TFB_ERR_INVALID_ARGUMENT, "contraction too large for one launch");
+    // one CTA per SM, so at most sm_count / 2 pairs run at once; each walks the work list with that stride
+    const int64_t grid = 2 * std::min<int64_t>(n_work, std::max(1, ctx->sm_count / 2));
     PoolBlock ws;
     if (g.k_split > 1) {
-        TFB_TRY(ws.alloc(ctx, (size_t)grid * Cfg::BN * kBM * sizeof(float)));
+        TFB_TRY(ws.alloc(ctx, (size_t)(2 * n_work) * Cfg::BN * kBM * sizeof(float)));
         g.partial = (float*)ws.ptr;
     }
     {
@@ -976,7 +1022,7 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     }
     if (g.k_split > 1) {
         LaunchScope ls(ctx, "contract_tf32x3_finish");
-        tf32x3_pair_splitk_finish_kernel<<<(unsigned)(2 * pair_tiles), 256, 0, ctx->stream>>>(g);
+        tf32x3_pair_splitk_finish_kernel<<<dim3((unsigned)(2 * pair_tiles), Cfg::BN / kFinishCols), 256, 0, ctx->stream>>>(g);
         TFB_CUDA(cudaGetLastError());
     }
     return TFB_OK;
