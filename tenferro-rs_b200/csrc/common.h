@@ -175,7 +175,7 @@ tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p);
 tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined,
                             const int64_t* const* c_tables = nullptr);
-tfb_status contract_c32_3m(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
+tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 
 // Scratch from the context pool, released stream-ordered when the object dies.
 struct PoolBlock {

@@ -295,7 +295,7 @@ tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_ker
     if (want == CK_AUTO || want == CK_TCGEN05) {
         if (p.dtype == TFB_F32 || p.dtype == TFB_C32) {
             if (p.dtype == TFB_C32)
-                TFB_TRY(contract_c32_3m(ctx, p, &declined));
+                TFB_TRY(contract_c32_embedded(ctx, p, &declined));
             else
                 TFB_TRY(contract_tcgen05(ctx, p, &declined));
             if (!declined) {

@@ -115,7 +115,7 @@ bool b_is_real_view(const ContractProblem& p) {
 
 }  // namespace
 
-tfb_status contract_c32_3m(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
+tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
     *declined = true;
     if (p.dtype != TFB_C32 || env_int("TFB_NO_TCGEN05", 0)) return TFB_OK;
     const int64_t M = p.M(), N = p.N(), K = p.K(), B = p.B();

@@ -1,12 +1,15 @@
 // f32 contraction on the 5th-generation tensor cores: TMA -> swizzled shared memory ->
 // 3xTF32 split -> tcgen05.mma (kind::tf32) into a TMEM accumulator -> epilogue.
 //
-// One CTA computes one 128 x BN tile of C (BN = 256 or 128).  Warp roles:
+// Two kernels share the scheme.  The CTA-pair kernel (further down) is the one large outputs
+// run on; the single-CTA kernel described first takes outputs with fewer than 129 rows or 256
+// columns.  One CTA computes one 128 x BN tile of C (BN = 256 or 128).  Warp roles:
 //   warp 0      TMA producer: one thread issues cp.async.bulk.tensor loads of the raw f32
 //               operand tiles straight from the strided tensors (the "permute" of
 //               permute-into-GEMM is the tensor map), 128-byte swizzle, zero fill at the edges;
-//   warps 2-9   split every element a into big = tf32(a) (written back in place) and
-//               small = a - big (second tile, same swizzled position);
+//   warps 2-9   split every element: the raw word serves as the truncated big part (the tensor
+//               core reads only its upper 19 bits); small = a - trunc(a), rounded to TF32, goes
+//               to a second tile at the same swizzled position;
 //   warp 1      one thread issues, per 8-deep k step, the three products
 //               small*big, big*small, big*big into the same TMEM accumulator - f32 accuracy
 //               from TF32 tensor cores (the dropped small*small term is ~2^-22 relative);
@@ -23,8 +26,10 @@
 // Operands may be K-major (contracted group has unit stride) or MN-major (free group has
 // unit stride); the instruction descriptor's major bits select the layout, so neither needs
 // a transpose pass.  Layouts TMA cannot describe (unit stride in neither group, strides that
-// are not multiples of 16 bytes, more than two non-fusable modes per group) are declined and
-// run on the SIMT kernel.
+// are not multiples of 16 bytes, more than two non-fusable modes per group) are repacked
+// K-major first when the product is large, and otherwise declined and run on the SIMT kernel.
+// Few tiles with a long K are split over K, with a finishing kernel that adds the partial
+// tiles in a fixed order.
 //
 // Semantics: PrimDescriptor::{Contract, BatchedGemm}, tenferro-prims/src/lib.rs:156-168, 227-239.
 #include <cuda.h>
@@ -61,8 +66,6 @@ struct TcArgs {
     int k_e1, k_blocks1, num_kb;  // inner K extent, k-blocks per inner K slice, k-blocks in total
     int64_t tiles_m, tiles_n;
     int group_m;                  // m-tiles per raster group (L2 reuse)
-    int elect;                    // 1: one lane per warp polls/arrives on mbarriers
-    int raw_big;                  // 1: leave the raw tile in place as the big operand (hardware truncation)
     int k_split, kb_per_split;    // split-K: CTAs per output tile, k-blocks per CTA
     float* partial;               // split-K: [tile][split][BN cols][128 rows] raw sums
     int* status;
@@ -99,11 +102,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
            (1ull << 46) | ((uint64_t)layout << 61);
 }
 
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return __uint_as_float(u);
-}
 
 // Raster of output tiles: m-tiles are visited in groups of `group_m` so that CTAs running
 // together share B panels (and the A panels of the group) through L2.
@@ -189,12 +187,12 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full(s), 1);
-            mbar_init(bar_split(s), g.elect ? kSplitThreads / 32 : kSplitThreads);
+            mbar_init(bar_split(s), kSplitThreads / 32);
             mbar_init(bar_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_chunk(b), 1);
-            mbar_init(bar_promoted(b), g.elect ? kSplitThreads / 32 : kSplitThreads);
+            mbar_init(bar_promoted(b), kSplitThreads / 32);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -309,7 +307,7 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         auto promote = [&](int chunk) {
             const int buf = chunk & 1;
             // one lane polls, the warp follows: mbarrier operations of 32 lanes on one word serialise
-            if (lane == 0 || !g.elect) mbar_wait(bar_chunk(buf), (uint32_t)(chunk >> 1) & 1, g.status, 0x104);
+            if (lane == 0) mbar_wait(bar_chunk(buf), (uint32_t)(chunk >> 1) & 1, g.status, 0x104);
             __syncwarp();
             tc_fence_after();
 #pragma unroll
@@ -322,45 +320,31 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0 || !g.elect) mbar_arrive(bar_promoted(buf));
+            if (lane == 0) mbar_arrive(bar_promoted(buf));
         };
         for (int kb = 0; kb < num_kb; ++kb) {
             const int s = kb % STAGES;
             const uint32_t use = kb / STAGES;
-            if (lane == 0 || !g.elect) mbar_wait(bar_full(s), use & 1, g.status, 0x103);
+            if (lane == 0) mbar_wait(bar_full(s), use & 1, g.status, 0x103);
             __syncwarp();
             char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
             char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
             constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
 #pragma unroll 4
             for (int c = t; c < CHUNKS; c += kSplitThreads) {
-                float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
-                float4 b, sm;
-                if (g.raw_big) {
-                    // the tensor core reads only the upper 19 bits of each f32: the raw tile
-                    // already is the truncated "big" operand, nothing to write back
-                    b.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-                    b.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-                    b.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-                    b.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-                } else {
-                    b.x = to_tf32(v.x); b.y = to_tf32(v.y); b.z = to_tf32(v.z); b.w = to_tf32(v.w);
-                    *reinterpret_cast<float4*>(big + (size_t)c * 16) = b;
-                }
-                // the remainder is exact in f32; rounding it to tf32 here keeps the hardware's
-                // truncation of it from adding a one-sided error
-                if (g.raw_big) {
-                    sm.x = remainder_rounded(v.x); sm.y = remainder_rounded(v.y);
-                    sm.z = remainder_rounded(v.z); sm.w = remainder_rounded(v.w);
-                } else {
-                    sm.x = to_tf32(v.x - b.x); sm.y = to_tf32(v.y - b.y);
-                    sm.z = to_tf32(v.z - b.z); sm.w = to_tf32(v.w - b.w);
-                }
+                const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
+                float4 sm;
+                // the tensor core reads only the upper 19 bits of each f32: the raw tile already is
+                // the truncated "big" operand; the remainder is exact in f32 and rounded to tf32
+                sm.x = remainder_rounded(v.x);
+                sm.y = remainder_rounded(v.y);
+                sm.z = remainder_rounded(v.z);
+                sm.w = remainder_rounded(v.w);
                 *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
             }
             fence_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
             __syncwarp();
-            if (lane == 0 || !g.elect) mbar_arrive(bar_split(s));
+            if (lane == 0) mbar_arrive(bar_split(s));
             // A chunk whose last k-block lies STAGES behind has certainly retired: the stage
             // just split could only be loaded after that k-block's MMAs freed it.
             while (next_promote < num_chunks &&
@@ -956,8 +940,6 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     g.tiles_m = tiles(g.a, g.M, kBM);
     g.tiles_n = tiles(g.b, g.N, BN);
     g.group_m = env_int("TFB_TC_GROUP_M", 16);
-    g.elect = env_int("TFB_TC_ELECT", 1);
-    g.raw_big = env_int("TFB_TC_RAWBIG", 1);
     const int64_t n_tiles = g.tiles_m * g.tiles_n * g.B;
     choose_k_split(&g, n_tiles, ctx->sm_count);
     const int64_t grid = n_tiles * g.k_split;
@@ -1001,8 +983,6 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     g.tiles_m = tiles(g.a, g.M, kBM);  // 128-row tiles; a pair takes two of each
     g.tiles_n = tiles(g.b, g.N, 128);
     g.group_m = env_int("TFB_TC_GROUP_M", 8);
-    g.elect = 1;
-    g.raw_big = 1;
     const int64_t pair_tiles = ((g.tiles_m + 1) / 2) * ((g.tiles_n + 1) / 2) * g.B;
     choose_k_split(&g, pair_tiles, ctx->sm_count / 2);
     const int64_t n_work = pair_tiles * g.k_split;
