@@ -174,7 +174,8 @@ tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_ker
 tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p);
 tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined,
-                            const int64_t* const* c_tables = nullptr);
+                            const int64_t* const* c_tables = nullptr, const std::vector<Mode>* c_n_modes = nullptr,
+                            int c_scale = 1);
 tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 
 // Scratch from the context pool, released stream-ordered when the object dies.

@@ -60,6 +60,10 @@ struct TcArgs {
     const int64_t* c_b;
     const int64_t* c_m;
     const int64_t* c_n;
+    // Column offsets in closed form when the N side of the output has at most two modes:
+    // offset(n) = (n % cn_e1) * cn_s1 + (n / cn_e1) * cn_s2; cn_e1 == 0: use the c_n table.
+    int cn_e1;
+    int64_t cn_s1, cn_s2;
     int64_t M, N, K, B;
     float alpha, beta;
     TcGeom a, b;
@@ -441,6 +445,35 @@ struct PairCfg {
     static_assert(kChunk >= STAGES, "promotion lag assumes a chunk spans at least the ring");
 };
 
+// Columns [Q, Q + 1) * ceil(N / SLICES) of one thread's row of finished sums.  Column offsets
+// follow the (at most two) output modes of the N side in closed form - no table loads in the
+// way; indices into `acc` are compile-time so the sums stay in registers.
+template <int Q, int SLICES, int N>
+__device__ __forceinline__ void store_acc_slice(const float (&acc)[N], float* row, int col0, int e1, int64_t s1, int64_t s2,
+                                                int valid, float alpha, float beta) {
+    constexpr int W = (N + SLICES - 1) / SLICES;
+    constexpr int j0 = Q * W;
+    if (j0 >= valid) return;
+    const bool read_c = beta != 0.f;
+    const int n0 = col0 + j0, outer = n0 / e1;
+    int inner = n0 - outer * e1;
+    float* p = row + inner * s1 + outer * s2;
+    const int64_t wrap = s2 - (int64_t)e1 * s1;
+#pragma unroll
+    for (int jj = 0; jj < W; ++jj) {
+        if (j0 + jj < N && j0 + jj < valid) {
+            float v = alpha * acc[j0 + jj < N ? j0 + jj : 0];
+            if (read_c) v += beta * *p;
+            *p = v;
+        }
+        p += s1;
+        if (++inner == e1) {
+            inner = 0;
+            p += wrap;
+        }
+    }
+}
+
 // One unit of work of a CTA pair: a 256 x 256 pair tile (128-row m-tiles 2 tmp, 2 tmp + 1, one per
 // CTA, x 128-column n-tiles 2 tnp, 2 tnp + 1) and, with split-K, one k range of it.
 struct PairWork {
@@ -630,18 +663,46 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         const uint32_t leader_split0 = map_to_cta(bar_split(0), 0), leader_promoted0 = map_to_cta(bar_promoted(0), 0);
         float acc[CPW];
         uint32_t it = 0, ch0 = 0;  // k-blocks and chunks handled before this work item
+        // Deferred epilogue.  All pairs finish their tiles at about the same time, so storing a
+        // tile right away makes every SM write at once while every tensor core waits.  The
+        // finished sums stay in `acc` instead and leave in kSlices slices, one after each of the
+        // next tile's first k-blocks (its first promotion, which needs `acc` cleared, comes
+        // later); what is left is flushed before that promotion.
+        constexpr int kSlices = 6;
+        float* pend_row = nullptr;   // &C[row, 0] of the pending tile, nullptr: nothing pending
+        int pend_col0 = 0;           // linear index of its first column
+        int pend_valid = 0, pend_next = kSlices;
+        auto store_slice = [&](int sl) {
+            // an if-chain on purpose: with a switch the compiler turns the slice number into an
+            // index and moves `acc` to local memory
+            if (sl == 0) store_acc_slice<0, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
+            else if (sl == 1) store_acc_slice<1, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
+            else if (sl == 2) store_acc_slice<2, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
+            else if (sl == 3) store_acc_slice<3, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
+            else if (sl == 4) store_acc_slice<4, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
+            else store_acc_slice<5, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
+        };
+        auto flush_pending = [&]() {
+            if (pend_row) {
+#pragma unroll
+                for (int sl = 0; sl < kSlices; ++sl)
+                    if (sl >= pend_next) store_slice(sl);
+                pend_next = kSlices;
+            }
+            pend_row = nullptr;
+        };
         auto promote = [&](uint32_t chunk) {
             const int buf = chunk & 1;
             if (lane == 0) mbar_wait(bar_chunk(buf), (chunk >> 1) & 1, g.status, 0x114);
             __syncwarp();
             tc_fence_after();
 #pragma unroll
-            for (int c0 = 0; c0 < CPW; c0 += 32) {
-                uint32_t r[32];
-                tc_ld32(tmem_mine + (uint32_t)(buf * BN + c0), r);
+            for (int c0 = 0; c0 < CPW; c0 += 16) {
+                uint32_t r[16];  // 16 columns at a time: the running sums need the registers
+                tc_ld16(tmem_mine + (uint32_t)(buf * BN + c0), r);
                 tc_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+                for (int j = 0; j < 16; ++j) acc[c0 + j] += __uint_as_float(r[j]);
             }
             tc_fence_before();
             __syncwarp();
@@ -652,10 +713,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         const int num_kb = pw.num_kb, num_chunks = (num_kb + kChunk - 1) / kChunk;
         const TileRows tr_m = pw.tr_m;
         const int64_t bb = pw.batch;
-#pragma unroll
-        for (int j = 0; j < CPW; ++j) acc[j] = 0.f;
-        int next_promote = 0;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        auto convert_block = [&]() {
             const int s = it % STAGES;
             const uint32_t use = it / STAGES;
             if (lane == 0) mbar_wait(bar_full(s), use & 1, g.status, 0x113);
@@ -677,6 +735,23 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_split0 + 8u * s);
+            ++it;
+        };
+        // No promotion of this tile is due before k-block kChunk - 1 + STAGES: until then `acc`
+        // still holds the previous tile, which leaves slice by slice.
+        constexpr int kQuiet = kChunk - 1 + STAGES;
+        static_assert(kQuiet >= kSlices, "every slice gets a k-block of its own");
+        int kb = 0;
+        for (; kb < num_kb && kb < kQuiet; ++kb) {
+            convert_block();
+            if (pend_row && pend_next < kSlices) store_slice(pend_next++);
+        }
+        flush_pending();
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) acc[j] = 0.f;
+        int next_promote = 0;
+        for (; kb < num_kb; ++kb) {
+            convert_block();
             while (next_promote < num_chunks &&
                    min((next_promote + 1) * kChunk, num_kb) - 1 + STAGES <= kb)
                 promote(ch0 + next_promote++);
@@ -686,26 +761,35 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
         const int row = lane_grp * 32 + lane;
         const TileRows trn = half ? pw.tr_n[1] : pw.tr_n[0];
-        if (g.k_split > 1) {
+        if (g.partial) {
             // raw partial sums of this CTA's 128 x 256 part, rows fastest
             float* P = g.partial + ((size_t)((pw.pair_tile * 2 + rank) * g.k_split + pw.split) * BN + col0) * kBM + row;
 #pragma unroll
             for (int j = 0; j < CPW; ++j) P[(size_t)j * kBM] = acc[j];
-        } else if (row < tr_m.valid) {
-            float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
-            const int64_t cm = g.c_m[tr_m.base + row];
-            const bool read_c = g.beta != 0.f;
+        } else if (row < tr_m.valid && trn.valid > 0) {
+            float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb] + g.c_m[tr_m.base + row];
+            if (g.cn_e1 != 0) {
+                // deferred: leaves in slices during the next tile's first k-blocks
+                pend_row = C;
+                pend_col0 = (int)trn.base;
+                pend_valid = trn.valid;
+                pend_next = 0;
+            } else {
+                // columns without a common stride: through the table, right away
+                const bool read_c = g.beta != 0.f;
 #pragma unroll
-            for (int j = 0; j < CPW; ++j) {
-                if (j < trn.valid) {
-                    float* p = C + cm + g.c_n[trn.base + j];
-                    float v = g.alpha * acc[j];
-                    if (read_c) v += g.beta * *p;
-                    *p = v;
+                for (int j = 0; j < CPW; ++j) {
+                    if (j < trn.valid) {
+                        float* p = C + g.c_n[trn.base + j];
+                        float v = g.alpha * acc[j];
+                        if (read_c) v += g.beta * *p;
+                        *p = v;
+                    }
                 }
             }
         }
         }
+        flush_pending();
     }
     tc_fence_before();
     cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still reach into it
@@ -990,7 +1074,8 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     // one CTA per SM, so at most sm_count / 2 pairs run at once; each walks the work list with that stride
     const int64_t grid = 2 * std::min<int64_t>(n_work, std::max(1, ctx->sm_count / 2));
     PoolBlock ws;
-    if (g.k_split > 1) {
+    const bool via_partials = g.k_split > 1;
+    if (via_partials) {
         TFB_TRY(ws.alloc(ctx, (size_t)(2 * n_work) * Cfg::BN * kBM * sizeof(float)));
         g.partial = (float*)ws.ptr;
     }
@@ -1000,7 +1085,7 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
         contract_tf32x3_pair_kernel<<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
         TFB_CUDA(cudaGetLastError());
     }
-    if (g.k_split > 1) {
+    if (via_partials) {
         LaunchScope ls(ctx, "contract_tf32x3_finish");
         tf32x3_pair_splitk_finish_kernel<<<dim3((unsigned)(2 * pair_tiles), Cfg::BN / kFinishCols), 256, 0, ctx->stream>>>(g);
         TFB_CUDA(cudaGetLastError());
@@ -1082,8 +1167,12 @@ extern "C" tfb_status tfb_probe_tf32_tflops(tfb_ctx* ctx, double* tflops) {
 
 // `c_tables`, when given, are device offset tables {batch, row, column} (in floats) that replace
 // the ones derived from p's output strides: the complex path writes into a complex tensor
-// through its f32 view this way.
-tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined, const int64_t* const* c_tables) {
+// through its f32 view this way; `c_n_modes` / `c_scale` then describe the column offsets in closed form
+// (the N modes of the complex problem, strides times 2).
+tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined, const int64_t* const* c_tables,
+                            const std::vector<Mode>* c_n_modes, int c_scale) {
+    const std::vector<Mode>* cn_modes = c_tables ? c_n_modes : &p.n;
+    if (!c_tables) c_scale = 1;
     *declined = true;
     if (p.dtype != TFB_F32) return TFB_OK;
     if (env_int("TFB_NO_TCGEN05", 0)) return TFB_OK;
@@ -1142,6 +1231,14 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     TcArgs g;
     memset(&g, 0, sizeof g);
     g.c = (char*)p.c;
+    // closed form of the output's column offsets (in floats; `c_scale` = 2 for the f32 view of a complex output)
+    g.cn_e1 = 0;
+    if (cn_modes && !cn_modes->empty() && cn_modes->size() <= 2 && (*cn_modes)[0].extent < INT32_MAX) {
+        const std::vector<Mode>& nm = *cn_modes;
+        g.cn_e1 = nm.size() == 2 ? (int)nm[0].extent : INT32_MAX;
+        g.cn_s1 = c_scale * nm[0].s[2];
+        g.cn_s2 = nm.size() == 2 ? c_scale * nm[1].s[2] : 0;
+    }
     if (c_tables) {
         g.c_b = c_tables[0]; g.c_m = c_tables[1]; g.c_n = c_tables[2];
     } else {
