@@ -125,7 +125,7 @@ __device__ __forceinline__ void load_panels(const Stage& u, float* As, float* Bs
 struct MmaPath {
     float acc[2][4][4], corr[2][4][4];
     int wm, wn;
-    bool live_i[2], live_j[4];
+    int ci, cj;  // live blocks of 16 rows (0..2) and of 8 columns (0..4) in this warp's part of the unit
 
     __device__ __forceinline__ void clear() {
 #pragma unroll
@@ -140,13 +140,14 @@ struct MmaPath {
         const int lw = cur.shape & 3, ni = (cur.shape >> 2) & 3, nj = (cur.shape >> 4) & 7;
         wm = (warp & ((1 << lw) - 1)) * 16 * ni;
         wn = (warp >> lw) * 8 * nj;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) live_i[i] = i < ni && wm + 16 * i < cur.mt;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) live_j[j] = j < nj && wn + 8 * j < cur.nt;
+        ci = max(0, min(ni, (cur.mt - wm + 15) / 16));
+        cj = max(0, min(nj, (cur.nt - wn + 7) / 8));
+        if (ci == 0 || cj == 0) ci = cj = 0;
     }
-    __device__ __forceinline__ void stage(const Stage& cur, const float* As, const float* Bs, int tid) {
-        if (!(live_i[0] && live_j[0])) return;
+    // One stage with NI x NJ blocks per warp, all live: the shapes are compile-time so that a small
+    // unit issues only its own instructions (predicated-off ones still take issue slots).
+    template <int NI, int NJ>
+    __device__ __forceinline__ void stage_t(const Stage& cur, const float* As, const float* Bs, int tid) {
         const int lane = tid & 31, gq = lane >> 2, tq = lane & 3;
         const int K = cur.k, LDB = K + LDBPAD;
         const float* pa = As + (2 * tq) * LDA + wm + 2 * gq;
@@ -157,63 +158,81 @@ struct MmaPath {
             // m16n8k16 MMA for both corrections, its 16-deep K holding small_a x big_b in the
             // first eight positions and big_a x small_b in the other eight.  The corrections are
             // 2^-11 of the product, so bf16's 2^-9 rounding of them lands at 2^-20.
-            uint32_t ab[2][4], ac[2][4], bb[4][2], bc[4][2];
+            uint32_t ab[NI][4], ac[NI][4], bb[NJ][2], bc[NJ][2];
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-                if (live_i[i]) {
-                    const float2 lo = *reinterpret_cast<const float2*>(pa + k0 * LDA + 16 * i);
-                    const float2 hi = *reinterpret_cast<const float2*>(pa + (k0 + 1) * LDA + 16 * i);
-                    ab[i][0] = __float_as_uint(lo.x); ab[i][1] = __float_as_uint(lo.y);
-                    ab[i][2] = __float_as_uint(hi.x); ab[i][3] = __float_as_uint(hi.y);
-                    ac[i][0] = pack_bf16(remainder_tf32(lo.x), remainder_tf32(hi.x));  // row g,     k 2t, 2t+1
-                    ac[i][1] = pack_bf16(remainder_tf32(lo.y), remainder_tf32(hi.y));  // row g + 8
-                    ac[i][2] = pack_bf16(lo.x, hi.x);                                  // row g,     k 8 + 2t, ...
-                    ac[i][3] = pack_bf16(lo.y, hi.y);                                  // row g + 8
-                }
+            for (int i = 0; i < NI; ++i) {
+                const float2 lo = *reinterpret_cast<const float2*>(pa + k0 * LDA + 16 * i);
+                const float2 hi = *reinterpret_cast<const float2*>(pa + (k0 + 1) * LDA + 16 * i);
+                ab[i][0] = __float_as_uint(lo.x); ab[i][1] = __float_as_uint(lo.y);
+                ab[i][2] = __float_as_uint(hi.x); ab[i][3] = __float_as_uint(hi.y);
+                ac[i][0] = pack_bf16(remainder_tf32(lo.x), remainder_tf32(hi.x));  // row g,     k 2t, 2t+1
+                ac[i][1] = pack_bf16(remainder_tf32(lo.y), remainder_tf32(hi.y));  // row g + 8
+                ac[i][2] = pack_bf16(lo.x, hi.x);                                  // row g,     k 8 + 2t, ...
+                ac[i][3] = pack_bf16(lo.y, hi.y);                                  // row g + 8
+            }
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (live_j[j]) {
-                    const float2 v = *reinterpret_cast<const float2*>(pb + 8 * j * LDB + k0);
-                    bb[j][0] = __float_as_uint(v.x); bb[j][1] = __float_as_uint(v.y);
-                    bc[j][0] = pack_bf16(v.x, v.y);
-                    bc[j][1] = pack_bf16(remainder_tf32(v.x), remainder_tf32(v.y));
-                }
+            for (int j = 0; j < NJ; ++j) {
+                const float2 v = *reinterpret_cast<const float2*>(pb + 8 * j * LDB + k0);
+                bb[j][0] = __float_as_uint(v.x); bb[j][1] = __float_as_uint(v.y);
+                bc[j][0] = pack_bf16(v.x, v.y);
+                bc[j][1] = pack_bf16(remainder_tf32(v.x), remainder_tf32(v.y));
+            }
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < NI; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (live_i[i] && live_j[j]) mma_bf16(corr[i][j], ac[i], bc[j]);
+                for (int j = 0; j < NJ; ++j) mma_bf16(corr[i][j], ac[i], bc[j]);
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < NI; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (live_i[i] && live_j[j]) mma_tf32(acc[i][j], ab[i], bb[j]);
+                for (int j = 0; j < NJ; ++j) mma_tf32(acc[i][j], ab[i], bb[j]);
         }
     }
     // A warp's store covers 64 contiguous bytes in each of 4 columns: whole sectors.
-    __device__ __forceinline__ void store(const Stage& cur, float alpha, float beta, int tid) {
+    template <int NI, int NJ>
+    __device__ __forceinline__ void store_t(const Stage& cur, float alpha, float beta, int tid) {
         const int lane = tid & 31, gq = lane >> 2, tq = lane & 3;
         const bool read_c = beta != 0.f;
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < NI; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < NJ; ++j)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int m = wm + 16 * i + 2 * gq, n = wn + 8 * j + 2 * tq + e;
-                    if (live_i[i] && live_j[j]) {
-                        float2* dst = reinterpret_cast<float2*>(cur.c + m + (int64_t)n * cur.c_cs);
-                        float2 v = make_float2(alpha * (acc[i][j][e] + corr[i][j][e]),
-                                               alpha * (acc[i][j][e + 2] + corr[i][j][e + 2]));
-                        if (read_c) {
-                            const float2 o = *dst;
-                            v.x += beta * o.x;
-                            v.y += beta * o.y;
-                        }
-                        *dst = v;
+                    float2* dst = reinterpret_cast<float2*>(cur.c + m + (int64_t)n * cur.c_cs);
+                    float2 v = make_float2(alpha * (acc[i][j][e] + corr[i][j][e]),
+                                           alpha * (acc[i][j][e + 2] + corr[i][j][e + 2]));
+                    if (read_c) {
+                        const float2 o = *dst;
+                        v.x += beta * o.x;
+                        v.y += beta * o.y;
                     }
+                    *dst = v;
                 }
     }
+#define TFB_GROUPED_SHAPES(CALL)                                                  \
+    switch (ci * 8 + cj) {                                                        \
+        case 1 * 8 + 1: CALL(1, 1); break;                                        \
+        case 1 * 8 + 2: CALL(1, 2); break;                                        \
+        case 1 * 8 + 3: CALL(1, 3); break;                                        \
+        case 1 * 8 + 4: CALL(1, 4); break;                                        \
+        case 2 * 8 + 1: CALL(2, 1); break;                                        \
+        case 2 * 8 + 2: CALL(2, 2); break;                                        \
+        case 2 * 8 + 3: CALL(2, 3); break;                                        \
+        case 2 * 8 + 4: CALL(2, 4); break;                                        \
+        default: break; /* this warp has no part of the unit */                   \
+    }
+    __device__ __forceinline__ void stage(const Stage& cur, const float* As, const float* Bs, int tid) {
+#define TFB_CALL(NI, NJ) stage_t<NI, NJ>(cur, As, Bs, tid)
+        TFB_GROUPED_SHAPES(TFB_CALL)
+#undef TFB_CALL
+    }
+    __device__ __forceinline__ void store(const Stage& cur, float alpha, float beta, int tid) {
+#define TFB_CALL(NI, NJ) store_t<NI, NJ>(cur, alpha, beta, tid)
+        TFB_GROUPED_SHAPES(TFB_CALL)
+#undef TFB_CALL
+    }
+#undef TFB_GROUPED_SHAPES
 };
 
 template <typename Path>
