@@ -484,8 +484,8 @@ def wl_grouped(env: Env):
         "peak": (lambda: hbm) if hbm else ctx.probe_hbm_gbs,
         "peak_source": "MEASURED_PEAKS.json hbm_gbs" if hbm else "library copy probe (MEASURED_PEAKS.json absent)",
         "extra_kernels": [], "keep": (a_t, b_t, c_t),
-        # profiles/grouped_tf32x3_ragged_4096.md: 121.7 MB read + 26.1 MB written
-        "traffic": 147.8e6 if (args.problems == 4096 and env.world == 1) else None,
+        # profiles/grouped_tf32x3_ragged_4096.md: 121.8 MB read + 25.5 MB written
+        "traffic": 147.3e6 if (args.problems == 4096 and env.world == 1) else None,
         "config": {"workload": f"{args.problems} problems 'ij,jk->ik', dims drawn from {{16,32,64,128}} (seed 3000), "
                                f"U(-1,1), f32", "parallelism": f"problem table split {env.world} ways by bytes",
                    "l2": f"inputs larger than L2: {bytes_all / 2**20:.0f} MiB touched per step",
