@@ -43,14 +43,19 @@ __device__ __forceinline__ int tile_off(int row, int k) {
 }
 
 template <typename Cfg, bool A_MN, bool B_MN>
-__device__ __forceinline__ void dmma_tma_consume(const char* sa, const char* sb, double (&acc)[Cfg::TM][Cfg::TN][Cfg::kCplx ? 4 : 2],
+__device__ __forceinline__ void dmma_tma_consume(const char* sa, const char* sb, double (&acc)[Cfg::TM][Cfg::TN][Cfg::kCplx ? 6 : 2],
                                                  int wm0, int wn0, int lr, int lc, bool conj_a, bool conj_b) {
     constexpr bool CPLX = Cfg::kCplx;
     constexpr int TM = Cfg::TM, TN = Cfg::TN;
 #pragma unroll
     for (int kk = 0; kk < Cfg::BK; kk += 8) {
         if (CPLX) {
-            double ar[TM][2], ai[TM][2], nai[TM][2], br[TN][2], bi[TN][2];
+            // Three real products per complex one instead of four:
+            //   P1 = Ar Br,  P2 = Ai Bi,  P3 = (Ar + Ai)(Br + Bi);  Re = P1 - P2,  Im = P3 - P1 - P2.
+            // The sums cost two adds per fragment element; the FP64 pipe, which is what this
+            // kernel waits for, issues a quarter fewer MMAs.  acc[..][0..1] = P1, [2..3] = P2,
+            // [4..5] = P3; the caller folds them into Re / Im when a k range ends.
+            double ar[TM][2], ai[TM][2], as[TM][2], br[TN][2], bi[TN][2], bs[TN][2];
 #pragma unroll
             for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -59,7 +64,7 @@ __device__ __forceinline__ void dmma_tma_consume(const char* sa, const char* sb,
                         sa + (size_t)tile_off<Cfg, Cfg::BM, A_MN>(wm0 + 8 * i + lr, kk + 4 * q + lc) * 16);
                     ar[i][q] = v.x;
                     ai[i][q] = conj_a ? -v.y : v.y;
-                    nai[i][q] = -ai[i][q];
+                    as[i][q] = ar[i][q] + ai[i][q];
                 }
 #pragma unroll
             for (int j = 0; j < TN; ++j)
@@ -69,6 +74,7 @@ __device__ __forceinline__ void dmma_tma_consume(const char* sa, const char* sb,
                         sb + (size_t)tile_off<Cfg, Cfg::BN, B_MN>(wn0 + 8 * j + lr, kk + 4 * q + lc) * 16);
                     br[j][q] = v.x;
                     bi[j][q] = conj_b ? -v.y : v.y;
+                    bs[j][q] = br[j][q] + bi[j][q];
                 }
 #pragma unroll
             for (int i = 0; i < TM; i += 2)
@@ -80,20 +86,14 @@ __device__ __forceinline__ void dmma_tma_consume(const char* sa, const char* sb,
             for (int i = 0; i < TM; i += 2)
 #pragma unroll
                 for (int j = 0; j < TN; ++j)
-                    dmma16(acc[i][j][2], acc[i][j][3], acc[i + 1][j][2], acc[i + 1][j][3], ar[i][0], ar[i + 1][0], ar[i][1],
-                           ar[i + 1][1], bi[j][0], bi[j][1]);
-#pragma unroll
-            for (int i = 0; i < TM; i += 2)
-#pragma unroll
-                for (int j = 0; j < TN; ++j)
-                    dmma16(acc[i][j][0], acc[i][j][1], acc[i + 1][j][0], acc[i + 1][j][1], nai[i][0], nai[i + 1][0],
-                           nai[i][1], nai[i + 1][1], bi[j][0], bi[j][1]);
-#pragma unroll
-            for (int i = 0; i < TM; i += 2)
-#pragma unroll
-                for (int j = 0; j < TN; ++j)
                     dmma16(acc[i][j][2], acc[i][j][3], acc[i + 1][j][2], acc[i + 1][j][3], ai[i][0], ai[i + 1][0], ai[i][1],
-                           ai[i + 1][1], br[j][0], br[j][1]);
+                           ai[i + 1][1], bi[j][0], bi[j][1]);
+#pragma unroll
+            for (int i = 0; i < TM; i += 2)
+#pragma unroll
+                for (int j = 0; j < TN; ++j)
+                    dmma16(acc[i][j][4], acc[i][j][5], acc[i + 1][j][4], acc[i + 1][j][5], as[i][0], as[i + 1][0], as[i][1],
+                           as[i + 1][1], bs[j][0], bs[j][1]);
         } else {
             double af[TM][2], bf[TN][2];
 #pragma unroll
@@ -185,13 +185,13 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int64_t ke = min(g.k_iters, kb + (it_end - it));
         const int64_t tm = tile % g.tiles_m, rest = tile / g.tiles_m, tn = rest % g.tiles_n, bb = rest / g.tiles_n;
         const int64_t m0 = tm * BM, n0 = tn * BN;
-        double acc[TM][TN][CPLX ? 4 : 2];
+        double acc[TM][TN][CPLX ? 6 : 2];
 #pragma unroll
         for (int i = 0; i < TM; ++i)
 #pragma unroll
             for (int j = 0; j < TN; ++j)
 #pragma unroll
-                for (int e = 0; e < (CPLX ? 4 : 2); ++e) acc[i][j][e] = 0.0;
+                for (int e = 0; e < (CPLX ? 6 : 2); ++e) acc[i][j][e] = 0.0;
 
         for (int64_t kit = kb; kit < ke; ++kit, ++n) {
             const int s = n % STAGES;
@@ -211,6 +211,19 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             if (lane == 0) mbar_arrive(bar_empty(s));
         }
 
+        if constexpr (CPLX) {
+            // fold the three products of this k range into Re (slots 0-1) and Im (slots 2-3)
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const double p1 = acc[i][j][e], p2 = acc[i][j][2 + e], p3 = acc[i][j][4 + e];
+                        acc[i][j][e] = p1 - p2;
+                        acc[i][j][2 + e] = p3 - p1 - p2;
+                    }
+        }
         // A range that starts inside a tile (kb > 0) only contributes: it parks its
         // accumulators in this CTA's scratch slot and raises the CTA's flag.  The range that
         // holds the tile's first k-iteration owns the tile: it collects the contributions of
