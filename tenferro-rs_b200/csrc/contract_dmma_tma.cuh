@@ -139,6 +139,10 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             mbar_init(bar_empty(s), Cfg::CONSUMERS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    } else if (tid == 32) {
+        // the two descriptors travel while the barriers are being set up
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     __syncthreads();
 
@@ -156,12 +160,15 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     auto produce_until = [&](int64_t target) {
         if (target > my_iters) target = my_iters;
         for (; issued < target; ++issued) {
-            const int64_t it_p = it_begin + issued;
-            const int64_t tile = it_p / g.k_iters, kit = it_p - tile * g.k_iters;
-            const int64_t tm = tile % g.tiles_m, rest = tile / g.tiles_m, tn = rest % g.tiles_n, bb = rest / g.tiles_n;
+            // 32-bit arithmetic: the host keeps total_iters below 2^31 for this kernel
+            const uint32_t it_p = (uint32_t)(it_begin + issued), k_iters = (uint32_t)g.k_iters;
+            const uint32_t tile = it_p / k_iters, kit = it_p - tile * k_iters;
+            const uint32_t tiles_m = (uint32_t)g.tiles_m, tiles_n = (uint32_t)g.tiles_n;
+            const uint32_t rest = tile / tiles_m, tm = tile - rest * tiles_m, bb = rest / tiles_n, tn = rest - bb * tiles_n;
             const int m0 = (int)(tm * BM), n0 = (int)(tn * BN), k0 = (int)(kit * BK);
-            const int s = (int)(issued % STAGES);
-            mbar_wait(bar_empty(s), (uint32_t)((issued / STAGES) & 1) ^ 1, status, 0x301);
+            const uint32_t iu = (uint32_t)issued;
+            const int s = (int)(iu % STAGES);
+            mbar_wait(bar_empty(s), ((iu / STAGES) & 1) ^ 1, status, 0x301);
             const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES, b_dst = a_dst + Cfg::A_BYTES;
             mbar_expect_tx(bar_full(s), Cfg::STAGE_BYTES);
             if (a_mn) tma_load_4d(a_dst, &map_a, bar_full(s), 0, k0, m0 / Cfg::G, (int)bb);
@@ -409,6 +416,7 @@ static tfb_status run_tma_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractAr
     a.n_tiles = a.tiles_m * a.tiles_n * a.B;
     a.k_iters = (a.K + Cfg::BK - 1) / Cfg::BK;
     a.total_iters = a.n_tiles * a.k_iters;
+    if (a.total_iters >= ((int64_t)1 << 31)) return TFB_OK;  // the producer indexes k-iterations with 32 bits
     const int64_t slots = ctx->sm_count;  // one CTA per SM
     int64_t grid;
     if (a.n_tiles % slots == 0 || a.n_tiles >= 16 * slots) {
