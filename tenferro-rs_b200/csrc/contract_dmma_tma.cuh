@@ -157,15 +157,23 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     constexpr int kLead = STAGES - 2;
     const int64_t my_iters = it_end - it_begin;
     int64_t issued = 0;
+    // Position of the next k-iteration to issue, advanced without divisions: the producer is also a
+    // computing thread, and whatever it spends here its whole warp waits for.  (32-bit: the host
+    // keeps total_iters below 2^31 for this kernel.)
+    uint32_t p_kit, p_tm, p_tn, p_bb;
+    {
+        const uint32_t k_iters = (uint32_t)g.k_iters, tiles_m = (uint32_t)g.tiles_m, tiles_n = (uint32_t)g.tiles_n;
+        const uint32_t tile = (uint32_t)it_begin / k_iters, rest = tile / tiles_m;
+        p_kit = (uint32_t)it_begin - tile * k_iters;
+        p_tm = tile - rest * tiles_m;
+        p_bb = rest / tiles_n;
+        p_tn = rest - p_bb * tiles_n;
+    }
     auto produce_until = [&](int64_t target) {
         if (target > my_iters) target = my_iters;
         for (; issued < target; ++issued) {
-            // 32-bit arithmetic: the host keeps total_iters below 2^31 for this kernel
-            const uint32_t it_p = (uint32_t)(it_begin + issued), k_iters = (uint32_t)g.k_iters;
-            const uint32_t tile = it_p / k_iters, kit = it_p - tile * k_iters;
-            const uint32_t tiles_m = (uint32_t)g.tiles_m, tiles_n = (uint32_t)g.tiles_n;
-            const uint32_t rest = tile / tiles_m, tm = tile - rest * tiles_m, bb = rest / tiles_n, tn = rest - bb * tiles_n;
-            const int m0 = (int)(tm * BM), n0 = (int)(tn * BN), k0 = (int)(kit * BK);
+            const int m0 = (int)(p_tm * BM), n0 = (int)(p_tn * BN), k0 = (int)(p_kit * BK);
+            const uint32_t bb = p_bb;
             const uint32_t iu = (uint32_t)issued;
             const int s = (int)(iu % STAGES);
             mbar_wait(bar_empty(s), ((iu / STAGES) & 1) ^ 1, status, 0x301);
@@ -175,6 +183,16 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             else      tma_load_4d(a_dst, &map_a, bar_full(s), 0, m0, k0 / 4, (int)bb);
             if (b_mn) tma_load_4d(b_dst, &map_b, bar_full(s), 0, k0, n0 / Cfg::G, (int)bb);
             else      tma_load_4d(b_dst, &map_b, bar_full(s), 0, n0, k0 / 4, (int)bb);
+            if (++p_kit == (uint32_t)g.k_iters) {
+                p_kit = 0;
+                if (++p_tm == (uint32_t)g.tiles_m) {
+                    p_tm = 0;
+                    if (++p_tn == (uint32_t)g.tiles_n) {
+                        p_tn = 0;
+                        ++p_bb;
+                    }
+                }
+            }
         }
     };
     const bool is_producer = (tid == 0);
