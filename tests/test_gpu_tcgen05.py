@@ -48,7 +48,7 @@ def test_tf32x3_is_far_better_than_plain_tf32(tb, oracle):
     got, name = run(tb, a, b, "row", "col", tb.ContractKernel.Tcgen05)
     assert name == "tcgen05_tf32x3"
     err = oracle.rel_frobenius(got, oracle.np_batched_gemm(a, b))
-    assert err <= 2e-6, err
+    assert err <= 3e-6, err
 
 
 def test_tf32x3_alpha_beta_and_batch(tb, oracle):
