@@ -117,10 +117,11 @@ struct LoopNest {
     int64_t total = 1;            // product of extents
 };
 
-// One mode of a normalised operation: extent and per-tensor element stride.
+// One mode of a normalised operation: extent and per-tensor element stride.  Tensors 0..2 are
+// the operation's own; slot 3 is the fused multiplier of a contraction (0 when there is none).
 struct Mode {
     int64_t extent;
-    int64_t s[3];
+    int64_t s[4];
 };
 
 // Sort `modes` by |stride| of tensor `key` ascending and fuse neighbours that are
@@ -153,6 +154,9 @@ tfb_status launch_scale(tfb_ctx* ctx, int dtype, const LoopNest& nest, void* out
 
 // Normalised contraction: C[b,m,n] = alpha * sum_k A[b,m,k] B[b,k,n] + beta * C.
 // Each group is a list of fused modes; tensor index 0 = A, 1 = B, 2 = C.
+// With `mul` set the sum is multiplied element-wise by D[b,m,n] (tensor index 3, broadcast
+// strides allowed) before alpha and beta apply: C = alpha * (A B) . D + beta * C.  This is the
+// einsum executor's fusion of a trailing Hadamard node into the product that feeds it.
 struct ContractProblem {
     int dtype = TFB_F64;
     std::vector<Mode> batch, m, n, k;
@@ -160,6 +164,8 @@ struct ContractProblem {
     const void* b = nullptr;
     void* c = nullptr;
     bool conj_a = false, conj_b = false;
+    const void* mul = nullptr;
+    bool conj_mul = false;
     Scalar alpha, beta;
     int64_t M() const;
     int64_t N() const;

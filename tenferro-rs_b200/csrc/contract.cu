@@ -60,6 +60,7 @@ static std::string signature(const ContractProblem& p) {
     put(p.m);
     put(p.n);
     put(p.k);
+    s.push_back(p.mul ? 'd' : '-');
     return s;
 }
 
@@ -87,8 +88,9 @@ tfb_status get_tables(tfb_ctx* ctx, const ContractProblem& p, std::shared_ptr<Co
     t->N = p.N();
     t->K = p.K();
     t->B = p.B();
-    // One allocation: a_b b_b c_b | a_m c_m | b_n c_n | a_k b_k
+    // One allocation: a_b b_b c_b | a_m c_m | b_n c_n | a_k b_k | d_b d_m d_n
     size_t n_entries = (size_t)(3 * t->B + 2 * t->M + 2 * t->N + 2 * t->K);
+    if (p.mul) n_entries += (size_t)(t->B + t->M + t->N);
     TFB_CUDA(cudaMalloc(&t->block, n_entries * sizeof(int64_t) + 64));
     int64_t* q = (int64_t*)t->block;
     t->a_b = q; q += t->B;
@@ -100,6 +102,11 @@ tfb_status get_tables(tfb_ctx* ctx, const ContractProblem& p, std::shared_ptr<Co
     t->c_n = q; q += t->N;
     t->a_k = q; q += t->K;
     t->b_k = q; q += t->K;
+    if (p.mul) {
+        t->d_b = q; q += t->B;
+        t->d_m = q; q += t->M;
+        t->d_n = q; q += t->N;
+    }
     TableJobs jobs;
     TFB_TRY(make_nest(p.batch, &jobs.job[0].nest));
     jobs.job[0].out[0] = t->a_b; jobs.job[0].out[1] = t->b_b; jobs.job[0].out[2] = t->c_b;
@@ -115,6 +122,27 @@ tfb_status get_tables(tfb_ctx* ctx, const ContractProblem& p, std::shared_ptr<Co
     LaunchScope ls(ctx, "build_tables");
     build_tables_kernel<<<dim3(gx, 4), 256, 0, ctx->stream>>>(jobs);
     TFB_CUDA(cudaGetLastError());
+    if (p.mul) {
+        // The multiplier's offsets over the same three output groups (its strides are slot 3).
+        auto slot3 = [](const std::vector<Mode>& g) {
+            std::vector<Mode> r;
+            for (auto& m : g) r.push_back(Mode{m.extent, {m.s[3], 0, 0}});
+            return r;
+        };
+        TableJobs dj;
+        TFB_TRY(make_nest(slot3(p.batch), &dj.job[0].nest));
+        TFB_TRY(make_nest(slot3(p.m), &dj.job[1].nest));
+        TFB_TRY(make_nest(slot3(p.n), &dj.job[2].nest));
+        TFB_TRY(make_nest(std::vector<Mode>{}, &dj.job[3].nest));
+        dj.job[3].nest.total = 0;
+        for (int j = 0; j < 4; ++j) dj.job[j].out[0] = dj.job[j].out[1] = dj.job[j].out[2] = nullptr;
+        dj.job[0].out[0] = t->d_b;
+        dj.job[1].out[0] = t->d_m;
+        dj.job[2].out[0] = t->d_n;
+        build_tables_kernel<<<dim3(gx, 4), 256, 0, ctx->stream>>>(dj);
+        count_launch();
+        TFB_CUDA(cudaGetLastError());
+    }
     // Bounded cache: drop the oldest entry once 256 layouts are held.  Tables in use by
     // enqueued kernels stay alive through cudaFree's implicit synchronisation.
     if (tc.order.size() >= 256) {
@@ -150,6 +178,9 @@ void fill_args(const ContractProblem& p, const ContractTables& t, ContractArgs* 
     a->beta_re = p.beta.re; a->beta_im = p.beta.im;
     a->conj_a = p.conj_a && dtype_is_complex(p.dtype);
     a->conj_b = p.conj_b && dtype_is_complex(p.dtype);
+    a->mul = (const char*)p.mul;
+    a->d_b = t.d_b; a->d_m = t.d_m; a->d_n = t.d_n;
+    a->conj_mul = p.conj_mul && dtype_is_complex(p.dtype);
     // Direction of the unit stride in each operand tile.  If neither group is unit-stride
     // the choice only affects which threads sit next to each other.
     bool a_k1 = group_unit_stride(p.k, 0), a_m1 = group_unit_stride(p.m, 0);
@@ -234,6 +265,7 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(ContractArgs g) {
         const T beta = Ops<T>::from(Scalar{g.beta_re, g.beta_im});
         const bool read_c = g.beta_re != 0 || g.beta_im != 0;
         T* Cb = C + g.c_b[bb];
+        const T* D = g.mul ? reinterpret_cast<const T*>(g.mul) + g.d_b[bb] : nullptr;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             int64_t n = n0 + ty + 16 * j;
@@ -244,7 +276,12 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(ContractArgs g) {
                 int64_t m = m0 + tx + 16 * i;
                 if (m >= g.M) continue;
                 T* p = Cb + g.c_m[m] + cn;
-                T v = Ops<T>::mul(alpha, acc[i][j]);
+                T sum = acc[i][j];
+                if (D) {
+                    const T d = D[g.d_m[m] + g.d_n[n]];
+                    sum = Ops<T>::mul(sum, g.conj_mul ? Ops<T>::conj(d) : d);
+                }
+                T v = Ops<T>::mul(alpha, sum);
                 if (read_c) v = Ops<T>::add(v, Ops<T>::mul(beta, *p));
                 *p = v;
             }

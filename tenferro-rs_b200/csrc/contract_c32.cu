@@ -17,7 +17,8 @@
 // Four real products' worth of MMAs instead of the three of the 3M scheme, but no product
 // planes (3 x M x N floats written and read again), no cancellation in the imaginary part, and
 // one launch of the f32 kernel whatever the output layout.  A complex beta that is not real is
-// applied by scaling C first.
+// applied by scaling C first.  A fused multiplier (ContractProblem::mul) is applied to C in
+// place after the product.
 //
 // Semantics: PrimDescriptor::{Contract, BatchedGemm} for Complex32,
 // tenferro-prims/src/lib.rs:156-168, 227-239.
@@ -115,7 +116,7 @@ bool b_is_real_view(const ContractProblem& p) {
 
 }  // namespace
 
-tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
+static tfb_status embedded_product(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
     *declined = true;
     if (p.dtype != TFB_C32 || env_int("TFB_NO_TCGEN05", 0)) return TFB_OK;
     const int64_t M = p.M(), N = p.N(), K = p.K(), B = p.B();
@@ -192,6 +193,27 @@ tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* d
     if (d) return fail(TFB_ERR_DEVICE, "internal: the embedded real product was declined by the tensor-core kernel");
     *declined = false;
     return TFB_OK;
+}
+
+tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
+    if (!p.mul) return embedded_product(ctx, p, declined);
+    // A fused multiplier is a complex product per element, and the real embedding holds the two
+    // parts of an element in different rows: the product runs unfused and C is multiplied in
+    // place afterwards (no intermediate tensor).  With a beta term the exact kernel takes it.
+    *declined = true;
+    if (!p.beta.is_zero()) return TFB_OK;
+    ContractProblem q = p;
+    q.mul = nullptr;
+    q.conj_mul = false;
+    TFB_TRY(embedded_product(ctx, q, declined));
+    if (*declined) return TFB_OK;
+    std::vector<Mode> all;
+    for (auto* g : {&p.m, &p.n, &p.batch})
+        for (auto& m : *g) all.push_back(Mode{m.extent, {m.s[2], m.s[3], m.s[2]}});
+    sort_and_fuse(all, 2, 3);
+    LoopNest nest;
+    TFB_TRY(make_nest(all, &nest));
+    return launch_elementwise_mul(ctx, p.dtype, nest, p.c, p.mul, p.c, Scalar{1.0, 0.0}, Scalar{0.0, 0.0}, false, p.conj_mul);
 }
 
 }  // namespace tfb

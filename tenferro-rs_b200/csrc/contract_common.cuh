@@ -30,6 +30,12 @@ struct ContractArgs {
     int64_t M, N, K, B;
     double alpha_re, alpha_im, beta_re, beta_im;
     int conj_a, conj_b;
+    // Fused trailing multiplier D[b,m,n] (nullptr: none): C = alpha * (A B) . D + beta * C.
+    const char* mul;
+    const int64_t* d_b;
+    const int64_t* d_m;
+    const int64_t* d_n;
+    int conj_mul;
     int a_kfast, b_kfast;  // 1: the unit-stride direction of the operand tile is K; 0: M (resp. N)
     int a_vec, b_vec;      // elements per cp.async (1, or 2 for f64 when 16-byte chunks are legal)
     // Work decomposition: tiles x k-iterations, cut into equal contiguous ranges ("stream-K").
@@ -39,6 +45,44 @@ struct ContractArgs {
     unsigned sk_epoch;   // a flag is raised when it equals this launch's epoch
     char* partial;  // 2 slots of one block tile per CTA, used only by ranges that cut a tile
 };
+
+// The fused multiplier's element at offset `off` (in elements), applied to a real or complex sum.
+__device__ __forceinline__ void apply_mul_f64(const ContractArgs& g, int64_t off, double& x) {
+    x *= *reinterpret_cast<const double*>(g.mul + off * 8);
+}
+__device__ __forceinline__ void apply_mul_c128(const ContractArgs& g, int64_t off, double& xr, double& xi) {
+    const double2 d = *reinterpret_cast<const double2*>(g.mul + off * 16);
+    const double di = g.conj_mul ? -d.y : d.y;
+    const double r = xr * d.x - xi * di;
+    xi = xr * di + xi * d.x;
+    xr = r;
+}
+
+// Multiplies a thread's m16n8 accumulator fragments (TM x TN of them, element (i, j, e) at row
+// m_first + 8 i, column n_first + 8 j + e; complex sums keep the imaginary part at [2 + e]) by the
+// fused multiplier, before anything is stored: with no store in between, all the loads are in flight
+// together.  A load placed after a store through an unrelated pointer would wait for that store.
+template <bool CPLX, int TM, int TN, int W>
+__device__ __forceinline__ void apply_mul_fragments(const ContractArgs& g, int64_t bb, int64_t m_first, int64_t n_first,
+                                                    double (&acc)[TM][TN][W]) {
+    const int64_t db = g.d_b[bb];
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int64_t n = n_first + 8 * j + e;
+            if (n >= g.N) continue;
+            const int64_t dn = db + g.d_n[n];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) {
+                const int64_t m = m_first + 8 * i;
+                if (m >= g.M) continue;
+                if constexpr (CPLX) apply_mul_c128(g, dn + g.d_m[m], acc[i][j][e], acc[i][j][2 + e]);
+                else apply_mul_f64(g, dn + g.d_m[m], acc[i][j][e]);
+            }
+        }
+    }
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);

@@ -282,6 +282,7 @@ __device__ __forceinline__ void dmma_range(const ContractArgs& g, char* smem, in
 
         const bool whole = (kb == 0 && ke == g.k_iters);
         if (whole) {
+            if (g.mul) apply_mul_fragments<CPLX>(g, bb, m0 + wm0 + lr, n0 + wn0 + 2 * lc, acc);
             char* Cb = g.c + g.c_b[bb] * (int64_t)ES;
             const bool read_c = g.beta_re != 0.0 || g.beta_im != 0.0;
 #pragma unroll
@@ -391,6 +392,11 @@ __global__ void __launch_bounds__(256) contract_dmma_fixup_kernel(ContractArgs g
             }
         }
         char* p = Cb + (g.c_m[m0 + ml] + g.c_n[n0 + nl]) * (int64_t)ES;
+        if (g.mul) {
+            const int64_t off = g.d_b[bb] + g.d_m[m0 + ml] + g.d_n[n0 + nl];
+            if (CPLX) apply_mul_c128(g, off, sr, si);
+            else apply_mul_f64(g, off, sr);
+        }
         if (CPLX) {
             double2 o;
             o.x = g.alpha_re * sr - g.alpha_im * si;

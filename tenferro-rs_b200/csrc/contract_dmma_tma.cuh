@@ -311,6 +311,7 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                             }
                 }
             }
+            if (g.mul) apply_mul_fragments<CPLX>(g, bb, m0 + wm0 + lr, n0 + wn0 + 2 * lc, acc);
             char* Cb = g.c + g.c_b[bb] * (int64_t)ES;
             const bool read_c = g.beta_re != 0.0 || g.beta_im != 0.0;
 #pragma unroll

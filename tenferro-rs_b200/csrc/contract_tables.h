@@ -10,6 +10,7 @@ struct ContractTables {
     void* block = nullptr;
     int64_t *a_b = nullptr, *b_b = nullptr, *c_b = nullptr;
     int64_t *a_m = nullptr, *c_m = nullptr, *b_n = nullptr, *c_n = nullptr, *a_k = nullptr, *b_k = nullptr;
+    int64_t *d_b = nullptr, *d_m = nullptr, *d_n = nullptr;  // the fused multiplier's offsets, when the problem has one
     int64_t M = 0, N = 0, K = 0, B = 0;
     ~ContractTables();
 };

@@ -64,8 +64,14 @@ struct TcArgs {
     // offset(n) = (n % cn_e1) * cn_s1 + (n / cn_e1) * cn_s2; cn_e1 == 0: use the c_n table.
     int cn_e1;
     int64_t cn_s1, cn_s2;
+    int64_t dn_s1, dn_s2;  // the same two modes in the fused multiplier
     int64_t M, N, K, B;
     float alpha, beta;
+    // Fused trailing multiplier D[b,m,n] (nullptr: none): C = alpha * (A B) . D + beta * C.
+    const float* mul;
+    const int64_t* d_b;
+    const int64_t* d_m;
+    const int64_t* d_n;
     TcGeom a, b;
     int k_e1, k_blocks1, num_kb;  // inner K extent, k-blocks per inner K slice, k-blocks in total
     int64_t tiles_m, tiles_n;
@@ -368,6 +374,13 @@ contract_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb];
             const int64_t cm = g.c_m[tr_m.base + row];
             const bool read_c = g.beta != 0.f;
+            if (g.mul) {
+                // multiplier values first, all loads in flight together (see store_acc_slice)
+                const float* D = g.mul + g.d_b[bb] + g.d_m[tr_m.base + row];
+#pragma unroll
+                for (int j = 0; j < CPW; ++j)
+                    if (col0 + j < tr_n.valid) acc[j] *= D[g.d_n[tr_n.base + col0 + j]];
+            }
 #pragma unroll
             for (int j = 0; j < CPW; ++j) {
                 const int col = col0 + j;
@@ -402,6 +415,7 @@ __global__ void __launch_bounds__(256) tf32x3_splitk_finish_kernel(TcArgs g) {
     const int64_t cm = g.c_m[tr_m.base + row];
     const bool read_c = g.beta != 0.f;
     const float* P = g.partial + (size_t)tile_id * g.k_split * BN * kBM + row;
+    const float* D = g.mul ? g.mul + g.d_b[bb] + g.d_m[tr_m.base + row] : nullptr;
     // blockIdx.y takes kFinishCols columns of the tile; two columns are in flight per pass
     const int col_end = min(tr_n.valid, (int)(blockIdx.y + 1) * kFinishCols);
     for (int col = blockIdx.y * kFinishCols + threadIdx.x / kBM; col < col_end; col += 256 / kBM) {
@@ -410,6 +424,7 @@ __global__ void __launch_bounds__(256) tf32x3_splitk_finish_kernel(TcArgs g) {
         for (int s = 0; s < g.k_split; ++s) sum += P[((size_t)s * BN + col) * kBM];
         float* p = C + cm + g.c_n[tr_n.base + col];
         float v = g.alpha * sum;
+        if (D) v *= D[g.d_n[tr_n.base + col]];
         if (read_c) v += g.beta * *p;
         *p = v;
     }
@@ -449,9 +464,10 @@ struct PairCfg {
 // Columns [Q, Q + 1) * ceil(N / SLICES) of one thread's row of finished sums.  Column offsets
 // follow the (at most two) output modes of the N side in closed form - no table loads in the
 // way; indices into `acc` are compile-time so the sums stay in registers.
-template <int Q, int SLICES, int N>
+template <int Q, int SLICES, int N, bool MUL>
 __device__ __forceinline__ void store_acc_slice(const float (&acc)[N], float* row, int col0, int e1, int64_t s1, int64_t s2,
-                                                int valid, float alpha, float beta) {
+                                                int valid, float alpha, float beta, const float* drow, int64_t ds1,
+                                                int64_t ds2) {
     constexpr int W = (N + SLICES - 1) / SLICES;
     constexpr int j0 = Q * W;
     if (j0 >= valid) return;
@@ -460,10 +476,29 @@ __device__ __forceinline__ void store_acc_slice(const float (&acc)[N], float* ro
     int inner = n0 - outer * e1;
     float* p = row + inner * s1 + outer * s2;
     const int64_t wrap = s2 - (int64_t)e1 * s1;
+    // The fused multiplier's row walks the same two modes with its own strides.  Its values are
+    // all fetched before the first store: a load issued after a store through an unrelated
+    // pointer would wait for it, and the slice would pay one memory round trip per column.
+    float dv[MUL ? W : 1];
+    if constexpr (MUL) {
+        int64_t d = inner * ds1 + outer * ds2;
+        const int64_t dwrap = ds2 - (int64_t)e1 * ds1;
+        int din = inner;
+#pragma unroll
+        for (int jj = 0; jj < W; ++jj) {
+            dv[jj] = (j0 + jj < N && j0 + jj < valid) ? drow[d] : 1.f;
+            d += ds1;
+            if (++din == e1) {
+                din = 0;
+                d += dwrap;
+            }
+        }
+    }
 #pragma unroll
     for (int jj = 0; jj < W; ++jj) {
         if (j0 + jj < N && j0 + jj < valid) {
             float v = alpha * acc[j0 + jj < N ? j0 + jj : 0];
+            if constexpr (MUL) v *= dv[jj];
             if (read_c) v += beta * *p;
             *p = v;
         }
@@ -504,6 +539,9 @@ __device__ __forceinline__ PairWork pair_work(const TcArgs& g, int64_t w, uint32
     return pw;
 }
 
+// MUL: the launch carries a fused multiplier (g.mul != nullptr).  A separate instantiation keeps the
+// multiplier's registers out of the plain kernel.
+template <bool MUL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + kSplitThreads, 1)
 contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
     using Cfg = PairCfg;
@@ -671,17 +709,18 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // later); what is left is flushed before that promotion.
         constexpr int kSlices = 6;
         float* pend_row = nullptr;   // &C[row, 0] of the pending tile, nullptr: nothing pending
+        const float* pend_drow = nullptr;  // the fused multiplier's row of that tile, nullptr: no multiplier
         int pend_col0 = 0;           // linear index of its first column
         int pend_valid = 0, pend_next = kSlices;
         auto store_slice = [&](int sl) {
             // an if-chain on purpose: with a switch the compiler turns the slice number into an
             // index and moves `acc` to local memory
-            if (sl == 0) store_acc_slice<0, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
-            else if (sl == 1) store_acc_slice<1, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
-            else if (sl == 2) store_acc_slice<2, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
-            else if (sl == 3) store_acc_slice<3, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
-            else if (sl == 4) store_acc_slice<4, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
-            else store_acc_slice<5, kSlices, CPW>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta);
+            if (sl == 0) store_acc_slice<0, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
+            else if (sl == 1) store_acc_slice<1, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
+            else if (sl == 2) store_acc_slice<2, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
+            else if (sl == 3) store_acc_slice<3, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
+            else if (sl == 4) store_acc_slice<4, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
+            else store_acc_slice<5, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
         };
         auto flush_pending = [&]() {
             if (pend_row) {
@@ -772,12 +811,19 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             if (g.cn_e1 != 0) {
                 // deferred: leaves in slices during the next tile's first k-blocks
                 pend_row = C;
+                if constexpr (MUL) pend_drow = g.mul + g.d_b[bb] + g.d_m[tr_m.base + row];
                 pend_col0 = (int)trn.base;
                 pend_valid = trn.valid;
                 pend_next = 0;
             } else {
                 // columns without a common stride: through the table, right away
                 const bool read_c = g.beta != 0.f;
+                if constexpr (MUL) {
+                    const float* D = g.mul + g.d_b[bb] + g.d_m[tr_m.base + row];
+#pragma unroll
+                    for (int j = 0; j < CPW; ++j)
+                        if (j < trn.valid) acc[j] *= D[g.d_n[trn.base + j]];
+                }
 #pragma unroll
                 for (int j = 0; j < CPW; ++j) {
                     if (j < trn.valid) {
@@ -815,6 +861,7 @@ __global__ void __launch_bounds__(256) tf32x3_pair_splitk_finish_kernel(TcArgs g
     const int64_t cm = g.c_m[tr_m.base + row];
     const bool read_c = g.beta != 0.f;
     const float* P = g.partial + (size_t)part * g.k_split * BN * kBM + row;
+    const float* D = g.mul ? g.mul + g.d_b[tc.batch] + g.d_m[tr_m.base + row] : nullptr;
     // blockIdx.y takes kFinishCols columns of one of the two 128-column halves
     {
         const int h = (int)(blockIdx.y * kFinishCols) / 128, j0 = (int)(blockIdx.y * kFinishCols) % 128;
@@ -827,6 +874,7 @@ __global__ void __launch_bounds__(256) tf32x3_pair_splitk_finish_kernel(TcArgs g
             for (int s = 0; s < g.k_split; ++s) sum += P[((size_t)s * BN + h * 128 + j) * kBM];
             float* p = C + cm + g.c_n[trn.base + j];
             float v = g.alpha * sum;
+            if (D) v *= D[g.d_n[trn.base + j]];
             if (read_c) v += g.beta * *p;
             *p = v;
         }
@@ -1054,7 +1102,9 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!configured[ctx->device]) {
-            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg::SMEM_BYTES));
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           Cfg::SMEM_BYTES));
             configured[ctx->device] = true;
         }
@@ -1083,7 +1133,10 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     {
         LaunchScope ls(ctx, "contract_tf32x3");
         // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
-        contract_tf32x3_pair_kernel<<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+        if (g.mul)
+            contract_tf32x3_pair_kernel<true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+        else
+            contract_tf32x3_pair_kernel<false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
         TFB_CUDA(cudaGetLastError());
     }
     if (via_partials) {
@@ -1239,12 +1292,19 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
         g.cn_e1 = nm.size() == 2 ? (int)nm[0].extent : INT32_MAX;
         g.cn_s1 = c_scale * nm[0].s[2];
         g.cn_s2 = nm.size() == 2 ? c_scale * nm[1].s[2] : 0;
+        g.dn_s1 = nm[0].s[3];
+        g.dn_s2 = nm.size() == 2 ? nm[1].s[3] : 0;
     }
     if (c_tables) {
         g.c_b = c_tables[0]; g.c_m = c_tables[1]; g.c_n = c_tables[2];
     } else {
         if (!t) TFB_TRY(get_tables(ctx, p, &t));
         g.c_b = t->c_b; g.c_m = t->c_m; g.c_n = t->c_n;
+    }
+    if (p.mul) {
+        if (!t) TFB_TRY(get_tables(ctx, p, &t));
+        g.mul = (const float*)p.mul;
+        g.d_b = t->d_b; g.d_m = t->d_m; g.d_n = t->d_n;
     }
     g.M = M; g.N = N; g.K = K; g.B = p.B();
     g.alpha = (float)p.alpha.re;

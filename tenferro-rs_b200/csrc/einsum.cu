@@ -529,8 +529,41 @@ tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t
         return labs;
     };
 
-    size_t next_id = n;
+    // A product whose only consumer multiplies it element-wise by a tensor that is already at
+    // hand (a tree node without summed labels, over the product's own labels) runs as ONE
+    // kernel: the multiplier is applied in the product's epilogue and the result goes straight
+    // to the consumer's destination.  Returns the consumer's step, or 0.
+    const bool fuse_mul = env_int("TFB_EINSUM_FUSE_MUL", 1) != 0;
+    auto fusable_consumer = [&](size_t s, const Live& x, const Live& y) -> size_t {
+        if (!fuse_mul) return 0;
+        const TreeStep& st = tree->steps[s];
+        const size_t id = n + s;
+        const LabelSet mine = unique_of(st.labels);
+        if (mine.size() != st.labels.size()) return 0;
+        bool summed = false;
+        for (auto lab : unique_of(x.labels))
+            if (has(unique_of(y.labels), lab) && !has(mine, lab)) summed = true;
+        if (!summed) return 0;
+        for (size_t c = s + 1; c < tree->steps.size(); ++c) {
+            const TreeStep& cs = tree->steps[c];
+            if (cs.lhs != id && cs.rhs != id) continue;
+            const size_t partner = cs.lhs == id ? cs.rhs : cs.lhs;
+            if (partner == id || partner == st.lhs || partner == st.rhs || !live.count(partner)) return 0;
+            const std::vector<uint32_t>& kept = (c + 1 == tree->steps.size()) ? out_labels : cs.labels;
+            const LabelSet kept_set = unique_of(kept);
+            if (kept_set.size() != kept.size() || kept_set.size() != mine.size()) return 0;
+            for (auto lab : mine)
+                if (!has(kept_set, lab)) return 0;
+            for (auto lab : live[partner].labels)
+                if (!has(mine, lab)) return 0;
+            return c;
+        }
+        return 0;
+    };
+
+    std::vector<char> done(tree->steps.size(), 0);
     for (size_t s = 0; s < tree->steps.size(); ++s) {
+        if (done[s]) continue;
         const TreeStep& st = tree->steps[s];
         if (!live.count(st.lhs) || !live.count(st.rhs)) return fail(TFB_ERR_INVALID_ARGUMENT, "corrupt contraction tree");
         TFB_TRY(presum(st.lhs, st.rhs));
@@ -538,18 +571,34 @@ tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t
         const bool last = s + 1 == tree->steps.size();
         Live& x = live[st.lhs];
         Live& y = live[st.rhs];
+        const size_t c = last ? 0 : fusable_consumer(s, x, y);
         if (last) {
             TFB_TRY(run_binary(ctx, dtype, x.labels, x.view, y.labels, y.view, out_labels, vout, a, b, 0, &used));
+        } else if (c != 0) {
+            const TreeStep& cs = tree->steps[c];
+            const size_t partner = cs.lhs == n + s ? cs.rhs : cs.lhs;
+            const Live& dmul = live[partner];
+            if (c + 1 == tree->steps.size()) {
+                TFB_TRY(run_binary(ctx, dtype, x.labels, x.view, y.labels, y.view, out_labels, vout, a, b, 0, &used,
+                                   &dmul.labels, &dmul.view));
+            } else {
+                Live t;
+                TFB_TRY(make_temp(temp_order(c), &t));
+                TFB_TRY(run_binary(ctx, dtype, x.labels, x.view, y.labels, y.view, t.labels, t.view, one, zero, 0, &used,
+                                   &dmul.labels, &dmul.view));
+                live[n + c] = t;
+            }
+            done[c] = 1;
+            live.erase(partner);
         } else {
             Live t;
             TFB_TRY(make_temp(temp_order(s), &t));
             TFB_TRY(run_binary(ctx, dtype, x.labels, x.view, y.labels, y.view, t.labels, t.view, one, zero, 0, &used));
-            live[next_id] = t;
+            live[n + s] = t;
         }
         // Intermediates go back to the pool in stream order as soon as their consumer is enqueued.
         live.erase(st.lhs);
         live.erase(st.rhs);
-        ++next_id;
     }
     return TFB_OK;
 }

@@ -175,12 +175,19 @@ tfb_status run_unary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& label
 // ------------------------------------------------------------------ binary
 tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labels_a, const HView& a,
                       const std::vector<uint32_t>& labels_b, const HView& b, const std::vector<uint32_t>& labels_c,
-                      const HView& c, Scalar alpha, Scalar beta, int force_kernel, const char** used) {
-    Labelled la, lb, lc;
-    bool ra = false, rb = false, rc = false;
+                      const HView& c, Scalar alpha, Scalar beta, int force_kernel, const char** used,
+                      const std::vector<uint32_t>* labels_d, const HView* d) {
+    Labelled la, lb, lc, ld;
+    bool ra = false, rb = false, rc = false, rd = false;
     TFB_TRY(merge_repeats(labels_a, a, &la, &ra, "first input"));
     TFB_TRY(merge_repeats(labels_b, b, &lb, &rb, "second input"));
     TFB_TRY(merge_repeats(labels_c, c, &lc, &rc, "output"));
+    if (d) {
+        TFB_TRY(merge_repeats(*labels_d, *d, &ld, &rd, "multiplier"));
+        for (auto l : ld.labels)
+            if (lc.find(l) < 0 || rc)
+                return fail(TFB_ERR_INVALID_ARGUMENT, "a fused multiplier may only carry labels of a plain output");
+    }
     if (c.conj) return fail(TFB_ERR_INVALID_ARGUMENT, "the output view cannot carry the conjugate flag");
     if (rc) {
         LoopNest all;
@@ -197,17 +204,25 @@ tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labe
     p.conj_b = b.conj;
     p.alpha = alpha;
     p.beta = beta;
+    if (d) {
+        p.mul = d->ptr;
+        p.conj_mul = d->conj;
+    }
     std::set<uint32_t> seen;
     auto classify = [&](uint32_t l) -> tfb_status {
         if (!seen.insert(l).second) return TFB_OK;
-        int ia = la.find(l), ib = lb.find(l), ic = lc.find(l);
+        int ia = la.find(l), ib = lb.find(l), ic = lc.find(l), id = d ? ld.find(l) : -1;
         int64_t e = ia >= 0 ? la.extent[ia] : ib >= 0 ? lb.extent[ib] : lc.extent[ic];
+        if (id >= 0 && ld.extent[id] != e)
+            return fail(TFB_ERR_SHAPE_MISMATCH, "shape mismatch: expected [%lld], got [%lld] (label %u)", (long long)e,
+                        (long long)ld.extent[id], l);
         if ((ia >= 0 && la.extent[ia] != e) || (ib >= 0 && lb.extent[ib] != e) || (ic >= 0 && lc.extent[ic] != e)) {
             int64_t got = (ib >= 0 && lb.extent[ib] != e) ? lb.extent[ib] : lc.extent[ic >= 0 ? ic : 0];
             return fail(TFB_ERR_SHAPE_MISMATCH, "shape mismatch: expected [%lld], got [%lld] (label %u)", (long long)e,
                         (long long)got, l);
         }
-        Mode m{e, {ia >= 0 ? la.stride[ia] : 0, ib >= 0 ? lb.stride[ib] : 0, ic >= 0 ? lc.stride[ic] : 0}};
+        Mode m{e, {ia >= 0 ? la.stride[ia] : 0, ib >= 0 ? lb.stride[ib] : 0, ic >= 0 ? lc.stride[ic] : 0,
+                   id >= 0 ? ld.stride[id] : 0}};
         if (ic >= 0) {
             if (ia >= 0 && ib >= 0)
                 p.batch.push_back(m);
@@ -241,11 +256,12 @@ tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labe
                 for (auto& m : *g) std::swap(m.s[0], m.s[1]);
         }
     }
-    sort_and_fuse(p.batch, 2, 3);
-    sort_and_fuse(p.m, 0, 3);
-    sort_and_fuse(p.n, 1, 3);
-    sort_and_fuse(p.k, 0, 3);
+    sort_and_fuse(p.batch, 2, 4);
+    sort_and_fuse(p.m, 0, 4);
+    sort_and_fuse(p.n, 1, 4);
+    sort_and_fuse(p.k, 0, 4);
     if (p.k.empty()) {
+        if (d) return fail(TFB_ERR_INVALID_ARGUMENT, "a fused multiplier needs a product with summed labels");
         // No summation: C[b,m,n] = alpha * A[b,m] * B[b,n] + beta * C is element-wise with
         // broadcast strides (Hadamard and outer products; PrimDescriptor::ElementwiseMul).
         std::vector<Mode> all;

@@ -20,8 +20,11 @@ tfb_status run_unary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& label
                      const std::vector<uint32_t>& labels_out, const HView& out, Scalar alpha, Scalar beta,
                      int reduce_op, const char** used);
 
+// With `d` the summed product is multiplied element-wise by d (labels a subset of the output's)
+// before alpha and beta apply: c = alpha * (a b) . d + beta * c.
 tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labels_a, const HView& a,
                       const std::vector<uint32_t>& labels_b, const HView& b, const std::vector<uint32_t>& labels_c,
-                      const HView& c, Scalar alpha, Scalar beta, int force_kernel, const char** used);
+                      const HView& c, Scalar alpha, Scalar beta, int force_kernel, const char** used,
+                      const std::vector<uint32_t>* labels_d = nullptr, const HView* d = nullptr);
 
 }  // namespace tfb
