@@ -541,7 +541,12 @@ __device__ __forceinline__ PairWork pair_work(const TcArgs& g, int64_t w, uint32
 
 // MUL: the launch carries a fused multiplier (g.mul != nullptr).  A separate instantiation keeps the
 // multiplier's registers out of the plain kernel.
-template <bool MUL>
+// SHORTK: every work item fits one TMEM accumulation chunk (K <= kChunk k-blocks, no split-K), so
+// the sums in tensor memory are final.  Half of the converter warps then only convert; the other
+// half only drain finished accumulators to the output (tcgen05.ld -> global stores).  Stores that
+// wait for the memory system no longer hold up the conversion the tensor cores are waiting for:
+// a short-K product writes its output at DRAM speed WHILE the next tiles are multiplied.
+template <bool MUL, bool SHORTK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + kSplitThreads, 1)
 contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
     using Cfg = PairCfg;
@@ -564,6 +569,8 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     constexpr int kWarps = kSplitThreads / 32;
+    // warps per CTA that arrive on the "converted" and on the "accumulator drained" barriers
+    constexpr int kRoleWarps = SHORTK ? kWarps / 2 : kWarps;
 
     // Persistent: this pair takes work items w0, w0 + wstep, ...  Every role walks the same
     // sequence with running counters (k-blocks for the stage ring, chunks for the two work
@@ -576,12 +583,12 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full(s), 1);
-            mbar_init(bar_split(s), 2 * kWarps);
+            mbar_init(bar_split(s), 2 * kRoleWarps);
             mbar_init(bar_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_chunk(b), 1);
-            mbar_init(bar_promoted(b), 2 * kWarps);
+            mbar_init(bar_promoted(b), 2 * kRoleWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -690,6 +697,93 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 }
             }
             ch0 += (uint32_t)((num_kb + kChunk - 1) / kChunk);
+            }
+        }
+    } else if constexpr (SHORTK) {
+        const uint32_t leader_split0 = map_to_cta(bar_split(0), 0), leader_promoted0 = map_to_cta(bar_promoted(0), 0);
+        if (warp < 2 + kRoleWarps) {
+            // ------------------------------------------------------------ converters only (warps 2-5)
+            constexpr int kConvThreads = kRoleWarps * 32;
+            const int t = threadIdx.x - 64;
+            uint32_t it = 0;
+            for (int64_t w = w0; w < n_work; w += wstep) {
+                const PairWork pw = pair_work(g, w, rank);
+                for (int kb = 0; kb < pw.num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t use = it / STAGES;
+                    if (lane == 0) mbar_wait(bar_full(s), use & 1, g.status, 0x113);
+                    __syncwarp();
+                    char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
+                    char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
+                    constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
+#pragma unroll 4
+                    for (int c = t; c < CHUNKS; c += kConvThreads) {
+                        const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
+                        float4 sm;
+                        sm.x = remainder_rounded(v.x);
+                        sm.y = remainder_rounded(v.y);
+                        sm.z = remainder_rounded(v.z);
+                        sm.w = remainder_rounded(v.w);
+                        *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(leader_split0 + 8u * s);
+                }
+            }
+        } else {
+            // ------------------------------------------------------------ drain warps (6-9): TMEM -> C
+            // One chunk per work item, so work item number = chunk number; the two accumulators
+            // alternate and the MMA thread reuses one only after all drain warps released it.
+            const int lane_grp = warp & 3;
+            const int row = lane_grp * 32 + lane;
+            const uint32_t tmem_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
+            const bool read_c = g.beta != 0.f;
+            uint32_t chunk = 0;
+            for (int64_t w = w0; w < n_work; w += wstep, ++chunk) {
+                const PairWork pw = pair_work(g, w, rank);
+                const int buf = chunk & 1;
+                if (lane == 0) mbar_wait(bar_chunk(buf), (chunk >> 1) & 1, g.status, 0x116);
+                __syncwarp();
+                tc_fence_after();
+                const bool live = row < pw.tr_m.valid;
+                float* C = reinterpret_cast<float*>(g.c);
+                if (live) C += g.c_b[pw.batch] + g.c_m[pw.tr_m.base + row];
+#pragma unroll 1
+                for (int h = 0; h < 2; ++h) {
+                    const TileRows trn = pw.tr_n[h];
+                    if (trn.valid <= 0) continue;  // warp-uniform: the whole half lies past the end
+                    // closed form of the column offsets (two output modes at most), else the table
+                    const bool closed = g.cn_e1 != 0;
+                    const int e1 = closed ? g.cn_e1 : 1;
+                    const int outer = closed ? (int)(trn.base / e1) : 0;
+                    int inner = closed ? (int)(trn.base - (int64_t)outer * e1) : 0;
+                    float* p = C + (closed ? inner * g.cn_s1 + outer * g.cn_s2 : 0);
+                    const int64_t wrap = g.cn_s2 - (int64_t)e1 * g.cn_s1;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < 128 && c0 < trn.valid; c0 += 16) {
+                        uint32_t r[16];
+                        tc_ld16(tmem_row + (uint32_t)(buf * BN + h * 128 + c0), r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (live && c0 + j < trn.valid) {
+                                float* q = closed ? p : C + g.c_n[trn.base + c0 + j];
+                                float v = g.alpha * __uint_as_float(r[j]);
+                                if (read_c) v += g.beta * *q;
+                                *q = v;
+                            }
+                            p += g.cn_s1;
+                            if (++inner == e1) {
+                                inner = 0;
+                                p += wrap;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_promoted0 + 8u * buf);
             }
         }
     } else {
@@ -1102,10 +1196,12 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!configured[ctx->device]) {
-            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg::SMEM_BYTES));
-            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg::SMEM_BYTES));
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<false, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<true, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<false, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
             configured[ctx->device] = true;
         }
     }
@@ -1133,10 +1229,14 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     {
         LaunchScope ls(ctx, "contract_tf32x3");
         // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
+        // short K, one accumulation chunk per tile: the variant with dedicated drain warps
+        const bool short_k = !g.mul && !via_partials && g.num_kb <= kChunk && env_int("TFB_TC_SHORTK", 1);
         if (g.mul)
-            contract_tf32x3_pair_kernel<true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+            contract_tf32x3_pair_kernel<true, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+        else if (short_k)
+            contract_tf32x3_pair_kernel<false, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
         else
-            contract_tf32x3_pair_kernel<false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+            contract_tf32x3_pair_kernel<false, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
         TFB_CUDA(cudaGetLastError());
     }
     if (via_partials) {

@@ -75,6 +75,38 @@ def test_cta_pair_tiles_odd_counts_and_ragged_edges(tb, oracle, shape, la, lb):
     assert oracle.rel_frobenius(got, oracle.np_batched_gemm(a, b, -1.5, 0.25, c0)) <= 1e-5
 
 
+@pytest.mark.parametrize("shape,beta,la,lb", [((4096, 4096, 72), 0.0, "col", "row"), ((2100, 4200, 250), 0.75, "col", "col"),
+                                              ((3, 600, 1100, 256), 0.0, "row", "row")])
+def test_short_k_products_drain_through_dedicated_warps(tb, oracle, shape, beta, la, lb, monkeypatch):
+    """K of at most 256: the sums in tensor memory are final, half of the converter warps only
+    drain them to the output while the other half keeps converting.  Several tiles per CTA pair, so
+    both accumulators are reused many times; ragged edges; beta; the same result, to rounding, as
+    the kernel that promotes and stores from the converter warps."""
+    *batch, m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a, b = random_array(rng, (*batch, m, k), np.float32), random_array(rng, (*batch, k, n), np.float32)
+    c0 = random_array(rng, (*batch, m, n), np.float32)
+    got, name = run(tb, a, b, la, lb, tb.ContractKernel.Auto, 1.25, beta, c0.copy())
+    assert name == "tcgen05_tf32x3"
+    want = oracle.np_batched_gemm(a, b, 1.25, beta, c0)
+    assert oracle.rel_frobenius(got, want) <= 1e-5
+    monkeypatch.setenv("TFB_TC_SHORTK", "0")
+    other, _ = run(tb, a, b, la, lb, tb.ContractKernel.Auto, 1.25, beta, c0.copy())
+    assert oracle.rel_frobenius(got, other) <= 2e-6
+
+
+def test_short_k_product_into_an_output_without_common_column_stride(tb, oracle):
+    """Three free modes on the N side: the drain warps take the column offsets from the table."""
+    rng = np.random.default_rng(77)
+    a = random_array(rng, (320, 64), np.float32)                    # [i, k]
+    b = random_array(rng, (64, 6, 10, 7), np.float32)               # [k, p, q, r]
+    plan = tb.CudaBackend.plan(tb.PrimDescriptor.Contract([0, 1], [1, 2, 3, 4], [3, 0, 4, 2]),
+                               [a.shape, b.shape, (10, 320, 7, 6)], np.float32)
+    out = tb.Tensor.zeros((10, 320, 7, 6), dtype=np.float32)
+    tb.CudaBackend.execute(plan, 1.0, [tb.Tensor.from_numpy(a), tb.Tensor.from_numpy(b)], 0.0, out)
+    assert oracle.rel_frobenius(out.to_numpy(), oracle.np_einsum("ik,kpqr->qirp", [a, b])) <= 1e-5
+
+
 @pytest.mark.parametrize("shape", [(96, 96, 9216), (96, 1000, 4096), (200, 120, 2052), (2, 130, 300, 1536)])
 def test_split_k_for_small_outputs_with_long_k(tb, oracle, shape):
     """Few output tiles and a long K: the k-blocks of a tile are shared out among several CTAs
