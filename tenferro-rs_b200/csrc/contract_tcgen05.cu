@@ -749,6 +749,9 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 const bool live = row < pw.tr_m.valid;
                 float* C = reinterpret_cast<float*>(g.c);
                 if (live) C += g.c_b[pw.batch] + g.c_m[pw.tr_m.base + row];
+                const float* D = g.mul;  // fused multiplier's row (MUL only)
+                if constexpr (MUL)
+                    if (live) D += g.d_b[pw.batch] + g.d_m[pw.tr_m.base + row];
 #pragma unroll 1
                 for (int h = 0; h < 2; ++h) {
                     const TileRows trn = pw.tr_n[h];
@@ -760,16 +763,33 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     int inner = closed ? (int)(trn.base - (int64_t)outer * e1) : 0;
                     float* p = C + (closed ? inner * g.cn_s1 + outer * g.cn_s2 : 0);
                     const int64_t wrap = g.cn_s2 - (int64_t)e1 * g.cn_s1;
+                    const float* d = D + (closed ? inner * g.dn_s1 + outer * g.dn_s2 : 0);
+                    const int64_t dwrap = g.dn_s2 - (int64_t)e1 * g.dn_s1;
 #pragma unroll 1
                     for (int c0 = 0; c0 < 128 && c0 < trn.valid; c0 += 16) {
                         uint32_t r[16];
                         tc_ld16(tmem_row + (uint32_t)(buf * BN + h * 128 + c0), r);
+                        float dv[MUL ? 16 : 1];
+                        if constexpr (MUL) {
+                            // the multiplier's 16 values, all requested before the first store
+                            int din = inner;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                dv[j] = (live && c0 + j < trn.valid) ? (closed ? *d : D[g.d_n[trn.base + c0 + j]]) : 1.f;
+                                d += g.dn_s1;
+                                if (++din == e1) {
+                                    din = 0;
+                                    d += dwrap;
+                                }
+                            }
+                        }
                         tc_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             if (live && c0 + j < trn.valid) {
                                 float* q = closed ? p : C + g.c_n[trn.base + c0 + j];
                                 float v = g.alpha * __uint_as_float(r[j]);
+                                if constexpr (MUL) v *= dv[j];
                                 if (read_c) v += g.beta * *q;
                                 *q = v;
                             }
@@ -1202,6 +1222,8 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
             TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<false, true>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<true, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
             configured[ctx->device] = true;
         }
     }
@@ -1230,8 +1252,10 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
         LaunchScope ls(ctx, "contract_tf32x3");
         // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
         // short K, one accumulation chunk per tile: the variant with dedicated drain warps
-        const bool short_k = !g.mul && !via_partials && g.num_kb <= kChunk && env_int("TFB_TC_SHORTK", 1);
-        if (g.mul)
+        const bool short_k = !via_partials && g.num_kb <= kChunk && env_int("TFB_TC_SHORTK", 1);
+        if (g.mul && short_k)
+            contract_tf32x3_pair_kernel<true, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+        else if (g.mul)
             contract_tf32x3_pair_kernel<true, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
         else if (short_k)
             contract_tf32x3_pair_kernel<false, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);

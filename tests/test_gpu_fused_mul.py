@@ -55,6 +55,7 @@ CASES = [
     ("ij,jk,i->ik", [(256, 512), (512, 384), (256,)], [(0, 1), (3, 2)]),         # ... along k, product on the right
     ("bij,bjk,bik->bik", [(3, 130, 64), (3, 64, 140), (3, 130, 140)], [(0, 1), (2, 3)]),
     ("ijl,jlk,ik->ik", [(257, 8, 33), (8, 33, 300), (257, 300)], [(0, 1), (2, 3)]),
+    ("ij,jk,ki->ik", [(700, 96), (96, 900), (900, 700)], [(0, 1), (2, 3)]),      # short K: the drain warps multiply
 ]
 
 
