@@ -539,6 +539,13 @@ __device__ __forceinline__ PairWork pair_work(const TcArgs& g, int64_t w, uint32
     return pw;
 }
 
+// The k-blocks of work item w alone (what pair_work reports as num_kb), without the tile decode and
+// its 64-bit divisions: all that the MMA thread and the converting warps need to know.
+__device__ __forceinline__ int pair_num_kb(const TcArgs& g, int64_t w) {
+    const int split = (int)(w % g.k_split);
+    return min(g.kb_per_split, g.num_kb - split * g.kb_per_split);
+}
+
 // MUL: the launch carries a fused multiplier (g.mul != nullptr).  A separate instantiation keeps the
 // multiplier's registers out of the plain kernel.
 // SHORTK: every work item fits one TMEM accumulation chunk (K <= kChunk k-blocks, no split-K), so
@@ -659,8 +666,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t a_step = g.a.mn_major ? 1024u : 32u, b_step = g.b.mn_major ? 1024u : 32u;
             uint32_t it = 0, ch0 = 0;  // k-blocks and chunks issued before this work item
             for (int64_t w = w0; w < n_work; w += wstep) {
-            const PairWork pw = pair_work(g, w, rank);
-            const int num_kb = pw.num_kb;
+            const int num_kb = pair_num_kb(g, w);
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t use = it / STAGES;
@@ -707,8 +713,8 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int t = threadIdx.x - 64;
             uint32_t it = 0;
             for (int64_t w = w0; w < n_work; w += wstep) {
-                const PairWork pw = pair_work(g, w, rank);
-                for (int kb = 0; kb < pw.num_kb; ++kb, ++it) {
+                const int num_kb = pair_num_kb(g, w);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t use = it / STAGES;
                     if (lane == 0) mbar_wait(bar_full(s), use & 1, g.status, 0x113);
