@@ -518,6 +518,10 @@ def wl_network4(env: Env):
         "peak_source": "one third of the library's dense TF32 probe: a complex multiply-add (8 flop) costs four real "
                        "ones, each three TF32 MMAs (24 TF32 flop)",
         "extra_kernels": ["pack_planes", "contract_tf32x3_finish"],
+        # ncu, per launch averaged over the three product launches of a call: the two large nodes moved
+        # 667 MB and 703 MB (profiles/contract_tf32x3_shortk_network4_c64.md); the third, whose operands
+        # (two 7 MB tensors) stay in L2, was not captured and is counted as zero
+        "traffic": (667.2e6 + 703.2e6) / 3.0 if dim == 96 else None,
         "config": {"workload": f"'{notation}' complex64, every index {dim}, N(0,1) parts; tree {tree.pairs}",
                    "parallelism": f"{env.world} independent replica(s)",
                    "l2": f"intermediates of {dim ** 4 * 8 >> 20} MiB exceed L2" if dim >= 64 else "L2-resident (scaled down)",
