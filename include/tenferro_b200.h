@@ -167,15 +167,21 @@ tfb_status tfb_ctx_destroy(tfb_ctx* ctx);
 tfb_status tfb_ctx_device(const tfb_ctx* ctx, int* device_id);
 /* The CUDA stream (cudaStream_t) all work of this context is enqueued on. */
 tfb_status tfb_ctx_stream(const tfb_ctx* ctx, void** stream);
-/* Enqueue on a caller-owned stream instead (NULL restores the context's own). */
+/* Enqueue on a caller-owned stream instead (NULL restores the context's own).  A context is ONE
+ * in-order queue: its pool blocks, cached offset tables and split-K scratch are ordered by "the
+ * context's stream", so the switch makes the new stream wait for everything already enqueued on
+ * the old one.  For work that should overlap (copies beside kernels) use a second context of
+ * the same device and chain the two with events. */
 tfb_status tfb_ctx_set_stream(tfb_ctx* ctx, void* stream);
 tfb_status tfb_ctx_synchronize(tfb_ctx* ctx);
 /* Number of SMs and bytes of device memory, as reported by the driver. */
 tfb_status tfb_ctx_properties(const tfb_ctx* ctx, int* sm_count, size_t* total_mem, int* cc_major, int* cc_minor);
 
-/* Stream-ordered allocation from the device's memory pool: the block is usable by
- * work enqueued after this call and is returned to the pool after work enqueued
- * before tfb_free has finished. */
+/* Stream-ordered allocation from the context's own memory pool (created with the context, not
+ * the device's default pool): the block is usable by work enqueued after this call and is
+ * returned to the pool after work enqueued before tfb_free has finished.  The environment
+ * variable TFB_POOL_BYTES, read when the context is created, caps the pool; an allocation
+ * past the cap returns TFB_ERR_DEVICE and the context stays usable. */
 tfb_status tfb_alloc(tfb_ctx* ctx, size_t bytes, void** out);
 tfb_status tfb_free(tfb_ctx* ctx, void* ptr);
 /* Bytes currently reserved / in use by the pool. */
@@ -184,6 +190,13 @@ tfb_status tfb_pool_stats(tfb_ctx* ctx, size_t* reserved, size_t* used);
 tfb_status tfb_memcpy_h2d_async(tfb_ctx* ctx, void* dst, const void* src, size_t bytes);
 tfb_status tfb_memcpy_d2h_async(tfb_ctx* ctx, void* dst, const void* src, size_t bytes);
 tfb_status tfb_memcpy_d2d_async(tfb_ctx* ctx, void* dst, const void* src, size_t bytes);
+/* Pitched copies: `height` rows of `width` bytes, consecutive rows `*_pitch` bytes apart.  This
+ * is how a slab of a strided host tensor (a range of one index of a column-major array) travels
+ * without a packing pass on the host. */
+tfb_status tfb_memcpy_h2d_2d_async(tfb_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                   size_t width, size_t height);
+tfb_status tfb_memcpy_d2h_2d_async(tfb_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                   size_t width, size_t height);
 /* GpuMemory{src_device} -> GpuMemory{dst_device} over NVLink
  * (Tensor::to_memory_space_async, tenferro-tensor/src/lib.rs:660-671). */
 tfb_status tfb_memcpy_p2p_async(tfb_ctx* ctx, void* dst, int dst_device, const void* src, int src_device, size_t bytes);
@@ -196,7 +209,8 @@ tfb_status tfb_host_free(void* ptr);
  * tfb_kernel_launch_count: kernels this library has launched in this process.
  * tfb_ctx_profile_begin/read/end: while on, every launch is bracketed by a CUDA event pair on
  * the launching stream; read() waits for the stream and returns the number of launches and
- * the summed device time of the kernel family `kernel` ("contract_dmma", "permute_tiled", ...).
+ * the summed device time of the kernel family `kernel` ("contract_dmma", "permute_tiled", ...),
+ * each pair's reading less what an empty pair reads (measured by begin()).
  * tfb_probe_*: peak probes - DMMA on register operands (TFLOP/s), streaming copy (GB/s). */
 unsigned long long tfb_kernel_launch_count(void);
 tfb_status tfb_ctx_profile_begin(tfb_ctx* ctx);
@@ -206,6 +220,15 @@ tfb_status tfb_probe_fp64_tflops(tfb_ctx* ctx, double* tflops);
 tfb_status tfb_probe_hbm_gbs(tfb_ctx* ctx, double* gbs);
 /* Dense TF32 rate of tcgen05.mma (128 x 256 x 8 tiles resident in shared memory), TFLOP/s. */
 tfb_status tfb_probe_tf32_tflops(tfb_ctx* ctx, double* tflops);
+/* The same loop launched back to back for `seconds` (at most 30); reports the rate of the last
+ * quarter of the run: what the tensor pipe sustains under the board's power limit. */
+tfb_status tfb_probe_tf32_tflops_sustained(tfb_ctx* ctx, double seconds, double* tflops);
+/* Self-test of the kernels' bounded waits (no counterpart in the reference): launches one CTA
+ * that waits, for at most `polls` polls (1..2^20), on an mbarrier nothing arrives on.  The wait
+ * runs out, the kernel records status code 0x7e57 and returns; the next tfb_ctx_synchronize
+ * reports TFB_ERR_DEVICE (Error::DeviceError, tenferro-device/src/lib.rs:128-130) with that code
+ * in the message and clears it, and the context keeps working. */
+tfb_status tfb_selftest_wait_expiry(tfb_ctx* ctx, unsigned polls);
 
 /* CompletionEvent (tenferro-tensor/src/lib.rs:301-309, 677-713). */
 tfb_status tfb_event_record(tfb_ctx* ctx, tfb_event** out);    /* marks all work enqueued so far */
@@ -239,9 +262,16 @@ tfb_status tfb_plan_destroy(tfb_plan* plan);
 /* Name of the kernel family the most recent tfb_execute of this plan used (for logs). */
 const char* tfb_plan_kernel_name(const tfb_plan* plan);
 /* Pin the contraction kernel family of a plan: 0 automatic (the default), 1 SIMT,
- * 2 FP64 tensor pipe (f64/c64), 3 tcgen05 3xTF32 (f32/c32).  "Pre-computes kernel
- * selection" (tenferro-prims/src/lib.rs:284-286) made visible so the families can be
- * checked against each other; a forced family that cannot run the layout is an error. */
+ * 2 FP64 tensor pipe (f64/c64), 3 tcgen05 3xTF32 (f32/c32), 4 FP64 tensor pipe with four real
+ * products per complex one.  "Pre-computes kernel selection" (tenferro-prims/src/lib.rs:284-286)
+ * made visible so the families can be checked against each other; a forced family that
+ * cannot run the layout is an error.
+ * About 4: by default a Complex64 product is formed from three real products (Re = P1 - P2,
+ * Im = (Ar+Ai)(Br+Bi) - P1 - P2).  The result is exact to a few ulp of its NORM, which is what
+ * the 1e-12 relative-Frobenius bound asks; but an imaginary part much smaller than the real part
+ * keeps only the digits it shares with it (|Im| = 1e-8 |Re|: about 8 of 16).  Kernel 4, or the
+ * environment variable TFB_C64_FOUR_PRODUCTS=1 for every Complex64 product including those of
+ * an einsum tree, computes Re and Im each to its own accuracy at roughly 3/4 of the speed. */
 tfb_status tfb_plan_force_kernel(tfb_plan* plan, int kernel);
 
 /* TensorPrims::execute (tenferro-prims/src/lib.rs:300-320):

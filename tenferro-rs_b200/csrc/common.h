@@ -63,7 +63,8 @@ struct tfb_ctx {
     int device = 0;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;  // own_stream or a caller-provided one
-    cudaMemPool_t pool = nullptr;
+    cudaMemPool_t pool = nullptr;  // the context's own pool (not the device's default one)
+    size_t pool_cap = 0;           // TFB_POOL_BYTES at creation, 0: uncapped
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
     size_t total_mem = 0;
@@ -78,6 +79,7 @@ struct tfb_ctx {
     unsigned sk_epoch = 0;
     // Optional per-launch timing (tfb_ctx_profile_*): event pairs around named launches.
     bool profiling = false;
+    float prof_pair_ms = 0;  // duration an empty event pair reports, subtracted from every launch
     struct ProfRec {
         const char* name;
         cudaEvent_t start, stop;
@@ -172,13 +174,15 @@ struct ContractProblem {
     int64_t K() const;
     int64_t B() const;
 };
-enum ContractKernel { CK_AUTO = 0, CK_SIMT = 1, CK_DMMA = 2, CK_TCGEN05 = 3 };
+// CK_DMMA4: the FP64 tensor pipe with FOUR real products per complex one (Complex64 only): slower
+// than the default three-product form, but Re and Im are each accurate to their own size.
+enum ContractKernel { CK_AUTO = 0, CK_SIMT = 1, CK_DMMA = 2, CK_TCGEN05 = 3, CK_DMMA4 = 4 };
 // Runs the problem on ctx's stream.  `used` receives the kernel family chosen.
 tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_kernel, const char** used);
 
 // Family-specific launchers (each may decline with *declined = true and TFB_OK).
 tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p);
-tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
+tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined, bool four_products = false);
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined,
                             const int64_t* const* c_tables = nullptr, const std::vector<Mode>* c_n_modes = nullptr,
                             int c_scale = 1);

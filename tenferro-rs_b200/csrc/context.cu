@@ -77,7 +77,12 @@ PoolBlock::~PoolBlock() {
 tfb_status PoolBlock::alloc(tfb_ctx* c, size_t bytes) {
     ctx = c;
     if (bytes == 0) bytes = 16;
-    TFB_CUDA(cudaMallocAsync(&ptr, bytes, c->stream));
+    cudaError_t e = cudaMallocFromPoolAsync(&ptr, bytes, c->pool, c->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        ptr = nullptr;
+        return fail(TFB_ERR_DEVICE, "pool allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    }
     return TFB_OK;
 }
 
@@ -114,7 +119,16 @@ tfb_status tfb_ctx_create(int device_id, tfb_ctx** out) {
         return fail(TFB_ERR_INVALID_ARGUMENT, "device_id %d out of range (have %d devices)", device_id, n);
     DeviceGuard g(device_id);
     if (!g.ok) return fail(TFB_ERR_DEVICE, "cudaSetDevice(%d) failed", device_id);
-    std::unique_ptr<tfb_ctx> c(new tfb_ctx);
+    // Frees whatever the context already owns when a later step of the set-up fails.
+    struct Cleanup {
+        void operator()(tfb_ctx* c) const {
+            if (c->own_stream) cudaStreamDestroy(c->own_stream);
+            if (c->dev_status) cudaFree(c->dev_status);
+            if (c->pool) cudaMemPoolDestroy(c->pool);
+            delete c;
+        }
+    };
+    std::unique_ptr<tfb_ctx, Cleanup> c(new tfb_ctx);
     c->device = device_id;
     cudaDeviceProp prop;
     TFB_CUDA(cudaGetDeviceProperties(&prop, device_id));
@@ -128,7 +142,20 @@ tfb_status tfb_ctx_create(int device_id, tfb_ctx** out) {
                     prop.major, prop.minor);
     TFB_CUDA(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
     c->stream = c->own_stream;
-    TFB_CUDA(cudaDeviceGetDefaultMemPool(&c->pool, device_id));
+    // A pool of the context's own: the device's default pool belongs to the host application,
+    // whose other cudaMallocAsync users would inherit any attribute set on it.  TFB_POOL_BYTES
+    // caps what the pool may hold (0 or unset: no cap); an allocation past the cap fails with
+    // DeviceError and leaves the context usable.
+    cudaMemPoolProps props;
+    memset(&props, 0, sizeof props);
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = device_id;
+    const char* cap = getenv("TFB_POOL_BYTES");
+    if (cap && *cap) props.maxSize = (size_t)strtoull(cap, nullptr, 10);
+    c->pool_cap = props.maxSize;
+    TFB_CUDA(cudaMemPoolCreate(&c->pool, &props));
     // Keep freed blocks cached in the pool instead of returning them to the driver at
     // every synchronisation: intermediates of a contraction tree are re-used each call.
     uint64_t threshold = UINT64_MAX;
@@ -148,6 +175,27 @@ tfb_status tfb_ctx_profile_begin(tfb_ctx* ctx) {
         cudaEventDestroy(r.stop);
     }
     ctx->prof.clear();
+    // What an event pair measures with nothing between its two records: the front end's cost
+    // of taking the two timestamps.  A pair around a launch contains the same cost on top of
+    // the kernel's run time, so profile_read subtracts it.
+    DeviceGuard g(ctx->device);
+    ctx->prof_pair_ms = 0;
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) == cudaSuccess) {
+        if (cudaEventCreate(&b) == cudaSuccess) {
+            float best = 1e30f;
+            for (int i = 0; i < 16; ++i) {
+                cudaEventRecord(a, ctx->stream);
+                cudaEventRecord(b, ctx->stream);
+                float ms = 0;
+                if (cudaEventSynchronize(b) == cudaSuccess && cudaEventElapsedTime(&ms, a, b) == cudaSuccess && ms < best)
+                    best = ms;
+            }
+            if (best < 1e29f) ctx->prof_pair_ms = best;
+            cudaEventDestroy(b);
+        }
+        cudaEventDestroy(a);
+    }
     ctx->profiling = true;
     return TFB_OK;
 }
@@ -163,7 +211,7 @@ tfb_status tfb_ctx_profile_read(tfb_ctx* ctx, const char* kernel, size_t* launch
         if (strcmp(r.name, kernel) != 0) continue;
         float ms = 0;
         TFB_CUDA(cudaEventElapsedTime(&ms, r.start, r.stop));
-        *total_ms += ms;
+        *total_ms += ms > ctx->prof_pair_ms ? ms - ctx->prof_pair_ms : 0.f;
         ++*launches;
     }
     return TFB_OK;
@@ -188,6 +236,7 @@ tfb_status tfb_ctx_destroy(tfb_ctx* ctx) {
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->sk_partial) cudaFree(ctx->sk_partial);
     if (ctx->sk_flags) cudaFree(ctx->sk_flags);
+    if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
     delete ctx;
     return TFB_OK;
 }
@@ -206,7 +255,19 @@ tfb_status tfb_ctx_stream(const tfb_ctx* ctx, void** stream) {
 
 tfb_status tfb_ctx_set_stream(tfb_ctx* ctx, void* stream) {
     if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_set_stream: ctx is NULL");
-    ctx->stream = stream ? (cudaStream_t)stream : ctx->own_stream;
+    cudaStream_t next = stream ? (cudaStream_t)stream : ctx->own_stream;
+    if (next == ctx->stream) return TFB_OK;
+    // Work enqueued on the new stream comes after everything already enqueued on the old one:
+    // pool blocks, the offset tables and the stream-K scratch of this context are all ordered
+    // by "the context's stream", so the switch must not let two of its launches overlap.
+    DeviceGuard g(ctx->device);
+    cudaEvent_t ev;
+    TFB_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaError_t e = cudaEventRecord(ev, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(next, ev, 0);
+    cudaEventDestroy(ev);
+    if (e != cudaSuccess) return fail(TFB_ERR_DEVICE, "tfb_ctx_set_stream: %s", cudaGetErrorString(e));
+    ctx->stream = next;
     return TFB_OK;
 }
 
@@ -238,8 +299,9 @@ tfb_status tfb_alloc(tfb_ctx* ctx, size_t bytes, void** out) {
     *out = nullptr;
     DeviceGuard g(ctx->device);
     if (bytes == 0) bytes = 16;
-    cudaError_t e = cudaMallocAsync(out, bytes, ctx->stream);
+    cudaError_t e = cudaMallocFromPoolAsync(out, bytes, ctx->pool, ctx->stream);
     if (e != cudaSuccess) {
+        *out = nullptr;
         cudaGetLastError();
         return fail(TFB_ERR_DEVICE, "pool allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
     }
@@ -283,6 +345,26 @@ tfb_status tfb_memcpy_d2h_async(tfb_ctx* ctx, void* dst, const void* src, size_t
 }
 tfb_status tfb_memcpy_d2d_async(tfb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     return do_copy(ctx, dst, src, bytes, cudaMemcpyDeviceToDevice, "tfb_memcpy_d2d_async");
+}
+
+static tfb_status do_copy_2d(tfb_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width,
+                             size_t height, cudaMemcpyKind kind, const char* who) {
+    if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", who);
+    if (width == 0 || height == 0) return TFB_OK;
+    if (!dst || !src) return fail(TFB_ERR_INVALID_ARGUMENT, "%s: NULL buffer", who);
+    if (dst_pitch < width || src_pitch < width)
+        return fail(TFB_ERR_INVALID_ARGUMENT, "%s: a pitch is smaller than the row width", who);
+    DeviceGuard g(ctx->device);
+    TFB_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, height, kind, ctx->stream));
+    return TFB_OK;
+}
+tfb_status tfb_memcpy_h2d_2d_async(tfb_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                   size_t width, size_t height) {
+    return do_copy_2d(ctx, dst, dst_pitch, src, src_pitch, width, height, cudaMemcpyHostToDevice, "tfb_memcpy_h2d_2d_async");
+}
+tfb_status tfb_memcpy_d2h_2d_async(tfb_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                   size_t width, size_t height) {
+    return do_copy_2d(ctx, dst, dst_pitch, src, src_pitch, width, height, cudaMemcpyDeviceToHost, "tfb_memcpy_d2h_2d_async");
 }
 
 tfb_status tfb_memcpy_p2p_async(tfb_ctx* ctx, void* dst, int dst_device, const void* src, int src_device,

@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(256) build_tables_kernel(TableJobs jobs) {
 
 ContractTables::~ContractTables() {
     if (block) cudaFree(block);
+    if (built) cudaEventDestroy(built);
 }
 
 static std::string signature(const ContractProblem& p) {
@@ -80,6 +81,18 @@ tfb_status get_tables(tfb_ctx* ctx, const ContractProblem& p, std::shared_ptr<Co
     std::lock_guard<std::mutex> lock(tc.mu);
     auto it = tc.map.find(key);
     if (it != tc.map.end()) {
+        ContractTables& hit = *it->second;
+        // Same stream as the build: stream order is enough.  Any other stream (another context
+        // of this device, or this context after tfb_ctx_set_stream) must not read the tables
+        // before the kernels that fill them have run.
+        if (!hit.ready && hit.built) {
+            if (cudaEventQuery(hit.built) == cudaSuccess) {
+                hit.ready = true;
+            } else {
+                cudaGetLastError();
+                if (ctx->stream != hit.build_stream) TFB_CUDA(cudaStreamWaitEvent(ctx->stream, hit.built, 0));
+            }
+        }
         *out = it->second;
         return TFB_OK;
     }
@@ -143,6 +156,9 @@ tfb_status get_tables(tfb_ctx* ctx, const ContractProblem& p, std::shared_ptr<Co
         count_launch();
         TFB_CUDA(cudaGetLastError());
     }
+    TFB_CUDA(cudaEventCreateWithFlags(&t->built, cudaEventDisableTiming));
+    TFB_CUDA(cudaEventRecord(t->built, ctx->stream));
+    t->build_stream = ctx->stream;
     // Bounded cache: drop the oldest entry once 256 layouts are held.  Tables in use by
     // enqueued kernels stay alive through cudaFree's implicit synchronisation.
     if (tc.order.size() >= 256) {
@@ -345,14 +361,15 @@ tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_ker
             return fail(TFB_ERR_INVALID_ARGUMENT, "tcgen05 kernel forced but the dtype is not f32/c32");
         }
     }
-    if (want == CK_AUTO || want == CK_DMMA) {
+    if (want == CK_AUTO || want == CK_DMMA || want == CK_DMMA4) {
         if (p.dtype == TFB_F64 || p.dtype == TFB_C64) {
-            TFB_TRY(contract_dmma(ctx, p, &declined));
+            const bool four = want == CK_DMMA4 || env_int("TFB_C64_FOUR_PRODUCTS", 0) != 0;
+            TFB_TRY(contract_dmma(ctx, p, &declined, four));
             if (!declined) {
                 if (used) *used = "dmma_f64";
                 return TFB_OK;
             }
-        } else if (want == CK_DMMA) {
+        } else if (want == CK_DMMA || want == CK_DMMA4) {
             return fail(TFB_ERR_INVALID_ARGUMENT, "DMMA kernel forced but the dtype is not f64/c64");
         }
     }

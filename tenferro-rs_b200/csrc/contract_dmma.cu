@@ -490,7 +490,7 @@ using RealSmall = DmmaCfg<false, 64, 64, 16, 2, 2, 4>;
 using CplxMain = DmmaCfg<true, 64, 64, 16, 4, 4, 4>;
 using CplxSmall = DmmaCfg<true, 32, 32, 8, 2, 2, 4>;
 
-tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
+tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined, bool four_products) {
     *declined = false;
     if (p.dtype != TFB_F64 && p.dtype != TFB_C64) {
         *declined = true;
@@ -523,7 +523,11 @@ tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined)
     bool small = (a.M <= 32 || a.N <= 32);
     if (shape == 1) small = true;
     if (shape == 2) small = false;
-    if (use_tma) {
+    // The TMA-fed kernel forms a complex product from three real ones, whose imaginary part is a
+    // difference of sums as large as the real part: norm-wise exact, but when |Im| << |Re| the
+    // imaginary part alone loses digits.  A caller that needs each part to its own accuracy asks
+    // for four products, which the gather kernel below computes.
+    if (use_tma && !four_products) {
         bool d = true;
         if (small)
             TFB_TRY(run_tma_cfg<CplxTmaSmall>(ctx, p, a, &d));

@@ -1349,6 +1349,46 @@ extern "C" tfb_status tfb_probe_tf32_tflops(tfb_ctx* ctx, double* tflops) {
     return TFB_OK;
 }
 
+// The same probe launched back to back for `seconds`: the rate of the last quarter of the run,
+// i.e. what the tensor pipe sustains once the power limit has pulled the clock down.  This is
+// the denominator for a kernel timed inside a long step; the burst figure above is the one for
+// a kernel timed alone.
+extern "C" tfb_status tfb_probe_tf32_tflops_sustained(tfb_ctx* ctx, double seconds, double* tflops) {
+    if (!ctx || !tflops) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_probe_tf32_tflops_sustained: NULL argument");
+    if (!(seconds > 0) || seconds > 30) return fail(TFB_ERR_INVALID_ARGUMENT, "seconds must be in (0, 30]");
+    DeviceGuard g(ctx->device);
+    const int smem = 16384 + 32768 + 64 + 1024;
+    TFB_CUDA(cudaFuncSetAttribute(probe_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    cudaEvent_t e0, e1;
+    TFB_CUDA(cudaEventCreate(&e0));
+    TFB_CUDA(cudaEventCreate(&e1));
+    const int iters = 20000, batch = 16;
+    const double flop_batch = (double)batch * ctx->sm_count * iters * 4 * (2.0 * 128 * 256 * 8);
+    std::vector<double> batch_ms;
+    double total_ms = 0;
+    tfb_status st = TFB_OK;
+    while (total_ms < seconds * 1e3 && batch_ms.size() < 4096) {
+        cudaEventRecord(e0, ctx->stream);
+        for (int i = 0; i < batch; ++i) probe_tf32_kernel<<<ctx->sm_count, 128, smem, ctx->stream>>>(iters, ctx->dev_status);
+        cudaEventRecord(e1, ctx->stream);
+        float ms = 0;
+        if (cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess || ms <= 0) {
+            st = fail(TFB_ERR_DEVICE, "tfb_probe_tf32_tflops_sustained: %s", cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        batch_ms.push_back(ms);
+        total_ms += ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (st != TFB_OK) return st;
+    const size_t tail = std::max<size_t>(1, batch_ms.size() / 4);
+    double ms_tail = 0;
+    for (size_t i = batch_ms.size() - tail; i < batch_ms.size(); ++i) ms_tail += batch_ms[i];
+    *tflops = flop_batch * tail / (ms_tail * 1e-3) / 1e12;
+    return TFB_OK;
+}
+
 // `c_tables`, when given, are device offset tables {batch, row, column} (in floats) that replace
 // the ones derived from p's output strides: the complex path writes into a complex tensor
 // through its f32 view this way; `c_n_modes` / `c_scale` then describe the column offsets in closed form

@@ -9,7 +9,24 @@
 #include <functional>
 #include <set>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "prims.h"
+
+// One NVTX range per tree node, so a timeline shows which kernels belong to which pairwise
+// contraction.  Without a profiler attached the calls return at once; TFB_NVTX=0 removes them.
+struct NodeRange {
+    bool on;
+    NodeRange(bool enabled, size_t step, size_t lhs, size_t rhs, bool fused) : on(enabled) {
+        if (!on) return;
+        char name[96];
+        snprintf(name, sizeof name, "tfb einsum node %zu: (%zu, %zu)%s", step, lhs, rhs, fused ? " + fused multiply" : "");
+        nvtxRangePushA(name);
+    }
+    ~NodeRange() {
+        if (on) nvtxRangePop();
+    }
+};
 
 // Nesting of operands given by parentheses: a leaf is an input index, a group is a list.
 struct Nest {
@@ -540,10 +557,12 @@ tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t
         const size_t id = n + s;
         const LabelSet mine = unique_of(st.labels);
         if (mine.size() != st.labels.size()) return 0;
-        bool summed = false;
+        // The product must really sum something: labels of extent 1 vanish when the modes are
+        // fused, and a product without a K group cannot carry a multiplier.
+        int64_t summed = 1;
         for (auto lab : unique_of(x.labels))
-            if (has(unique_of(y.labels), lab) && !has(mine, lab)) summed = true;
-        if (!summed) return 0;
+            if (has(unique_of(y.labels), lab) && !has(mine, lab)) summed *= tree->extent.at(lab);
+        if (summed <= 1) return 0;
         for (size_t c = s + 1; c < tree->steps.size(); ++c) {
             const TreeStep& cs = tree->steps[c];
             if (cs.lhs != id && cs.rhs != id) continue;
@@ -562,6 +581,7 @@ tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t
     };
 
     std::vector<char> done(tree->steps.size(), 0);
+    const bool nvtx = env_int("TFB_NVTX", 1) != 0;
     for (size_t s = 0; s < tree->steps.size(); ++s) {
         if (done[s]) continue;
         const TreeStep& st = tree->steps[s];
@@ -572,6 +592,7 @@ tfb_status tfb_einsum_with_plan_into(tfb_ctx* ctx, const tfb_tree* tree, int32_t
         Live& x = live[st.lhs];
         Live& y = live[st.rhs];
         const size_t c = last ? 0 : fusable_consumer(s, x, y);
+        NodeRange range(nvtx, s, st.lhs, st.rhs, c != 0);
         if (last) {
             TFB_TRY(run_binary(ctx, dtype, x.labels, x.view, y.labels, y.view, out_labels, vout, a, b, 0, &used));
         } else if (c != 0) {

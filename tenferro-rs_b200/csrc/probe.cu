@@ -1,6 +1,7 @@
 // Peak probes for the roofline denominators that no library call measures: the FP64 tensor
 // pipe (DMMA) on register-resident operands, and a plain streaming copy for HBM.
 #include "common.h"
+#include "ptx_sm100.cuh"
 
 namespace tfb {
 
@@ -28,11 +29,40 @@ __global__ void __launch_bounds__(256) probe_copy_kernel(const uint4* __restrict
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = in[i];
 }
 
+// Self-test of the bounded wait every kernel here relies on: one CTA sets up an mbarrier that
+// nothing ever arrives on, waits for it with a small poll limit, and returns.  The wait must
+// run out, leave its code in the status word and let the kernel end normally.
+constexpr int kSelftestWaitCode = 0x7e57;
+__global__ void __launch_bounds__(32) selftest_wait_expiry_kernel(int* status, unsigned polls, unsigned* polls_done) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        mbar_wait(b, 0, status, kSelftestWaitCode, polls);
+        if (polls_done) *polls_done = polls;
+    }
+}
+
 }  // namespace tfb
 
 using namespace tfb;
 
 extern "C" {
+
+tfb_status tfb_selftest_wait_expiry(tfb_ctx* ctx, unsigned polls) {
+    if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_selftest_wait_expiry: ctx is NULL");
+    if (polls == 0 || polls > (1u << 20))
+        return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_selftest_wait_expiry: polls must be in 1..2^20 (a short wait)");
+    DeviceGuard g(ctx->device);
+    LaunchScope ls(ctx, "selftest_wait_expiry");
+    selftest_wait_expiry_kernel<<<1, 32, 0, ctx->stream>>>(ctx->dev_status, polls, nullptr);
+    TFB_CUDA(cudaGetLastError());
+    return TFB_OK;
+}
 
 tfb_status tfb_probe_fp64_tflops(tfb_ctx* ctx, double* tflops) {
     if (!ctx || !tflops) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_probe_fp64_tflops: NULL argument");

@@ -30,9 +30,11 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after kSpinLimit polls, leaving `code` in the status word.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Bounded wait: gives up after `limit` polls (the kernels pass kSpinLimit), leaving `code` in
+// the status word.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* status, int code,
+                                          uint32_t limit = kSpinLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try(bar, parity)) return;
         // Once any wait of this launch has given up, the others stop waiting too.
         if ((i & 1023u) == 1023u && *(volatile int*)status != 0) return;

@@ -704,7 +704,18 @@ extern "C" tfb_status tfb_reduce_static(tfb_ctx* ctx, int32_t dtype, int32_t red
     for (auto& m : kept) kept_total *= m.extent;
     for (auto& m : red) red_total *= m.extent;
     if (kept_total == 0) return TFB_OK;
-    if (red_total == 0) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_reduce_static: the reduced range is empty");
+    if (red_total == 0) {
+        // As a Reduce plan does: the sum over nothing is 0, so C = beta * C (one launch, no
+        // scratch); Max/Min over nothing have no value.
+        if (reduce_op != TFB_REDUCE_SUM)
+            return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_reduce_static: Max/Min over an empty range is undefined");
+        sort_and_fuse(kept, 1, 2);
+        for (auto& m : kept) m.s[0] = m.s[1];
+        LoopNest nk0;
+        TFB_TRY(make_nest(kept, &nk0));
+        DeviceGuard guard0(ctx->device);
+        return launch_scale(ctx, dtype, nk0, vc.ptr, load_scalar(dtype, beta));
+    }
     const size_t out_bytes = (size_t)kept_total * dtype_size(dtype);
     if (out_bytes > kStaticReduceBytes / 2)
         return fail(TFB_ERR_INVALID_ARGUMENT,

@@ -81,6 +81,8 @@ PROTOTYPES = {
     "tfb_memcpy_h2d_async": (C.c_int, [_VP, _VP, _VP, C.c_size_t]),
     "tfb_memcpy_d2h_async": (C.c_int, [_VP, _VP, _VP, C.c_size_t]),
     "tfb_memcpy_d2d_async": (C.c_int, [_VP, _VP, _VP, C.c_size_t]),
+    "tfb_memcpy_h2d_2d_async": (C.c_int, [_VP, _VP, C.c_size_t, _VP, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "tfb_memcpy_d2h_2d_async": (C.c_int, [_VP, _VP, C.c_size_t, _VP, C.c_size_t, C.c_size_t, C.c_size_t]),
     "tfb_memcpy_p2p_async": (C.c_int, [_VP, _VP, C.c_int, _VP, C.c_int, C.c_size_t]),
     "tfb_memset_async": (C.c_int, [_VP, _VP, C.c_int, C.c_size_t]),
     "tfb_host_alloc": (C.c_int, [C.c_size_t, _VPP]),
@@ -92,6 +94,8 @@ PROTOTYPES = {
     "tfb_probe_fp64_tflops": (C.c_int, [_VP, C.POINTER(C.c_double)]),
     "tfb_probe_hbm_gbs": (C.c_int, [_VP, C.POINTER(C.c_double)]),
     "tfb_probe_tf32_tflops": (C.c_int, [_VP, C.POINTER(C.c_double)]),
+    "tfb_probe_tf32_tflops_sustained": (C.c_int, [_VP, C.c_double, C.POINTER(C.c_double)]),
+    "tfb_selftest_wait_expiry": (C.c_int, [_VP, C.c_uint]),
     "tfb_event_record": (C.c_int, [_VP, _VPP]),
     "tfb_event_wait": (C.c_int, [_VP, _VP]),
     "tfb_event_synchronize": (C.c_int, [_VP]),

@@ -171,6 +171,13 @@ class Context:
     def d2h(self, dst, src: int, nbytes: int) -> None:
         check(lib.tfb_memcpy_d2h_async(self.handle, dst, C.c_void_p(src), nbytes))
 
+    def h2d_2d(self, dst: int, dst_pitch: int, src, src_pitch: int, width: int, height: int) -> None:
+        """`height` rows of `width` bytes from (pinned) host memory, rows `*_pitch` bytes apart."""
+        check(lib.tfb_memcpy_h2d_2d_async(self.handle, C.c_void_p(dst), dst_pitch, src, src_pitch, width, height))
+
+    def d2h_2d(self, dst, dst_pitch: int, src: int, src_pitch: int, width: int, height: int) -> None:
+        check(lib.tfb_memcpy_d2h_2d_async(self.handle, dst, dst_pitch, C.c_void_p(src), src_pitch, width, height))
+
     def d2d(self, dst: int, src: int, nbytes: int) -> None:
         check(lib.tfb_memcpy_d2d_async(self.handle, C.c_void_p(dst), C.c_void_p(src), nbytes))
 
@@ -204,6 +211,8 @@ class Context:
         return s.value or 0
 
     def set_stream(self, stream: Optional[int]) -> None:
+        """Enqueue on a caller-owned stream from now on.  The new stream first waits for what is
+        already enqueued: a context is one in-order queue.  Overlap needs a second `Context`."""
         check(lib.tfb_ctx_set_stream(self.handle, C.c_void_p(stream or 0)))
 
     def properties(self):
@@ -233,6 +242,15 @@ class Context:
         v = C.c_double()
         check(lib.tfb_probe_tf32_tflops(self.handle, C.byref(v)))
         return v.value
+
+    def probe_tf32_tflops_sustained(self, seconds: float = 4.0) -> float:
+        v = C.c_double()
+        check(lib.tfb_probe_tf32_tflops_sustained(self.handle, float(seconds), C.byref(v)))
+        return v.value
+
+    def selftest_wait_expiry(self, polls: int = 4096) -> None:
+        """Launch the kernel whose bounded wait must run out; the next synchronize() raises DeviceError."""
+        check(lib.tfb_selftest_wait_expiry(self.handle, polls))
 
     def probe_hbm_gbs(self) -> float:
         v = C.c_double()

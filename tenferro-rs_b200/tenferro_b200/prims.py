@@ -13,7 +13,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import lib
-from .device import Context, InvalidArgument, check
+from .device import Context, InvalidArgument, NoCompatibleComputeDevice, check
 from .tensor import Tensor, check_same_space, dtype_code
 
 
@@ -37,6 +37,7 @@ class ContractKernel(enum.IntEnum):
     Simt = 1
     Dmma = 2
     Tcgen05 = 3
+    Dmma4 = 4  # Complex64 with four real products per complex one: Re and Im each to their own accuracy
 
 
 _OPS = {"BatchedGemm": 0, "Reduce": 1, "Trace": 2, "Permute": 3, "AntiTrace": 4, "AntiDiag": 5, "Contract": 6,
@@ -173,7 +174,10 @@ class CudaBackend:
         for t in tensors:
             if t.dtype != plan.dtype:
                 raise InvalidArgument(f"plan was made for {plan.dtype}, got a {t.dtype} tensor")
-        check_same_space(tensors)
+        space = check_same_space(tensors)
+        if not space.is_gpu:
+            raise NoCompatibleComputeDevice(
+                "no compatible compute device on MainMemory: move the tensors with to_memory_space_async first")
         ctx = plan.ctx
         for t in inputs:
             if t.event is not None and t.ctx is not ctx:

@@ -65,11 +65,37 @@ class _Block:
         self.ctx = ctx
         self.nbytes = nbytes
         self.ptr = ctx.alloc(nbytes)
+        self.event: Optional[CompletionEvent] = None  # latest write; shared by every view of the block
 
     def __del__(self):
         try:
             if self.ptr:
                 self.ctx.free(self.ptr)
+                self.ptr = 0
+        except Exception:
+            pass
+
+
+class _HostBlock:
+    """Page-locked main memory (`LogicalMemorySpace::MainMemory`): the staging end of
+    `to_memory_space_async`.  No kernel of this backend computes on it."""
+
+    def __init__(self, nbytes: int):
+        self.ctx = None
+        self.nbytes = nbytes
+        self.ptr = Context.host_alloc(max(nbytes, 16))
+        self.event: Optional[CompletionEvent] = None
+
+    def array(self, dtype) -> np.ndarray:
+        n = self.nbytes // np.dtype(dtype).itemsize
+        return np.ctypeslib.as_array((C.c_char * self.nbytes).from_address(self.ptr)).view(dtype)[:n]
+
+    def __del__(self):
+        try:
+            if self.ptr:
+                if self.event is not None:
+                    self.event.synchronize()  # a copy may still be reading or writing the buffer
+                Context.host_free(self.ptr)
                 self.ptr = 0
         except Exception:
             pass
@@ -81,6 +107,7 @@ class _Borrowed:
 
     def __init__(self, ctx: Context, ptr: int, nbytes: int, owner):
         self.ctx, self.ptr, self.nbytes, self.owner = ctx, ptr, nbytes, owner
+        self.event: Optional[CompletionEvent] = None
 
 
 def make_view(ptr: int, dims, strides, offset: int, conj: bool, keep: list) -> _lib.TfbView:
@@ -103,8 +130,23 @@ class Tensor:
         self.dtype = np.dtype(dtype)
         self._space = space
         self._preferred = preferred
-        self.event: Optional[CompletionEvent] = event
+        self._event: Optional[CompletionEvent] = None  # used only by storage-less (metadata) tensors
+        if event is not None:
+            self.event = event
         self._conj = bool(conj) and self.dtype.kind == "c"
+
+    @property
+    def event(self) -> Optional[CompletionEvent]:
+        """Completion of the latest write to the buffer (tenferro-tensor/src/lib.rs:301-309).  It
+        lives on the storage block, so a view taken before a later write still sees that write."""
+        return self._block.event if self._block is not None else self._event
+
+    @event.setter
+    def event(self, ev: Optional[CompletionEvent]) -> None:
+        if self._block is not None:
+            self._block.event = ev
+        else:
+            self._event = ev
 
     # ------------------------------------------------------------ constructors
     @staticmethod
@@ -117,9 +159,11 @@ class Tensor:
     @classmethod
     def empty(cls, dims, dtype=np.float64, memory_space=LogicalMemorySpace.GpuMemory(0),
               order=MemoryOrder.ColumnMajor) -> "Tensor":
-        ctx = cls._ctx_of(memory_space)
         n = int(np.prod(dims, dtype=np.int64)) if len(dims) else 1
-        block = _Block(ctx, max(n, 1) * np.dtype(dtype).itemsize)
+        if not memory_space.is_gpu:
+            block = _HostBlock(max(n, 1) * np.dtype(dtype).itemsize)
+        else:
+            block = _Block(cls._ctx_of(memory_space), max(n, 1) * np.dtype(dtype).itemsize)
         return cls(block, dims, contiguous_strides(dims, order), 0, dtype, memory_space)
 
     @classmethod
@@ -127,6 +171,9 @@ class Tensor:
               dtype=np.float64) -> "Tensor":
         """tenferro-tensor/src/lib.rs:336."""
         t = cls.empty(dims, dtype, memory_space, order)
+        if not memory_space.is_gpu:
+            t._block.array(np.uint8)[:] = 0
+            return t
         t._block.ctx.memset(t._block.ptr, 0, t._block.nbytes)
         t.event = t._block.ctx.record_event()
         return t
@@ -146,6 +193,11 @@ class Tensor:
         n = int(np.prod(dims, dtype=np.int64)) if len(dims) else 1
         if data.size != n:
             raise ShapeMismatch(f"shape mismatch: expected {list(dims)} ({n} elements), got {data.size} elements")
+        if not memory_space.is_gpu:
+            # MainMemory: a page-locked staging buffer; compute needs to_memory_space_async first
+            block = _HostBlock(max(n, 1) * data.dtype.itemsize)
+            block.array(data.dtype)[:n] = data
+            return cls(block, dims, contiguous_strides(dims, order), 0, data.dtype, memory_space)
         t = cls.empty(dims, data.dtype, memory_space, order)
         ctx = t._block.ctx
         if n:
@@ -222,7 +274,7 @@ class Tensor:
 
     def _derive(self, dims, strides, offset=None, conj=None) -> "Tensor":
         return Tensor(self._block, dims, strides, self._offset if offset is None else offset, self.dtype,
-                      self._space, self._preferred, self.event, self._conj if conj is None else conj)
+                      self._space, self._preferred, None, self._conj if conj is None else conj)
 
     def as_operand_view(self, keep: list) -> _lib.TfbView:
         """Non-blocking operand view (tenferro-tensor/src/lib.rs:473-488): pending work is
@@ -337,21 +389,47 @@ class Tensor:
         return self._derive(self._dims, self._strides, conj=not self._conj)
 
     def to_memory_space_async(self, target: LogicalMemorySpace) -> "Tensor":
-        """tenferro-tensor/src/lib.rs:660-671.  GPU -> GPU goes over NVLink; no-op when equal."""
+        """tenferro-tensor/src/lib.rs:660-671.  Same space: zero-copy (self comes back).  Main ->
+        GPU and GPU -> Main copy through page-locked memory; GPU -> GPU goes over NVLink.  The
+        call only enqueues; the result's event completes when the copy has landed."""
         if target == self._space:
             return self
-        if not target.is_gpu or not self._space.is_gpu:
-            raise NoCompatibleComputeDevice("this backend keeps tensors in GPU memory; use to_numpy()/from_numpy()")
-        src = self.into_contiguous(self._order() or MemoryOrder.ColumnMajor)
-        dst = Tensor.empty(src._dims, src.dtype, target, src._order() or MemoryOrder.ColumnMajor)
-        dctx = dst.ctx
-        if src.event is not None:
-            dctx.wait_event(src.event)
+        if not self._space.is_gpu:
+            # MainMemory -> GpuMemory: host tensors are always dense (from_slice made them)
+            order = self._order() or MemoryOrder.ColumnMajor
+            dst = Tensor.empty(self._dims, self.dtype, target, order)
+            dctx = dst.ctx
+            if self.len():
+                dctx.h2d(dst._block.ptr, C.c_void_p(self._block.ptr), self.len() * self.dtype.itemsize)
+            dst.event = dctx.record_event()
+            self._block.event = dst.event  # the staging buffer is busy until the copy has read it
+            dst._conj = self._conj
+            dst._keepalive = self
+            return dst
+        src = self if self._order() is not None else self.into_contiguous(MemoryOrder.ColumnMajor)
+        order = src._order() or MemoryOrder.ColumnMajor
         nbytes = src.len() * src.dtype.itemsize
+        src_ptr = src._block.ptr + src._offset * src.dtype.itemsize
+        if not target.is_gpu:
+            # GpuMemory -> MainMemory, on the source's stream (ordered behind its producer)
+            block = _HostBlock(max(nbytes, 1))
+            sctx = src.ctx
+            if nbytes:
+                sctx.d2h(C.c_void_p(block.ptr), src_ptr, nbytes)
+            dst = Tensor(block, src._dims, contiguous_strides(src._dims, order), 0, src.dtype, target, conj=src._conj)
+            dst.event = sctx.record_event()
+            dst._keepalive = src
+            return dst
+        dst = Tensor.empty(src._dims, src.dtype, target, order)
+        dctx = dst.ctx
+        # the copy runs on the destination's stream: it must come after the latest write to the
+        # source buffer, whichever view of it that write went through
+        ev = src.event if src.event is not None else src.ctx.record_event()
+        dctx.wait_event(ev)
         check(lib.tfb_memcpy_p2p_async(dctx.handle, C.c_void_p(dst._block.ptr), target.space_id,
-                                       C.c_void_p(src._block.ptr + src._offset * src.dtype.itemsize),
-                                       src._space.space_id, nbytes))
+                                       C.c_void_p(src_ptr), src._space.space_id, nbytes))
         dst.event = dctx.record_event()
+        dst._conj = src._conj
         dst._keepalive = src  # the source block must outlive the copy
         return dst
 
@@ -366,13 +444,17 @@ class Tensor:
 
     def to_numpy(self) -> np.ndarray:
         """Host copy of the logical contents (waits for pending work)."""
-        ctx = self.ctx
-        ctx.synchronize()
         if self.len() == 0:
             return np.zeros(self._dims, dtype=self.dtype)
-        raw = np.empty(self._block.nbytes // self.dtype.itemsize, dtype=self.dtype)
-        ctx.d2h(raw.ctypes.data_as(C.c_void_p), self._block.ptr, raw.nbytes)
-        ctx.synchronize()
+        if not self._space.is_gpu:
+            self.wait()
+            raw = self._block.array(self.dtype).copy()
+        else:
+            ctx = self.ctx
+            ctx.synchronize()
+            raw = np.empty(self._block.nbytes // self.dtype.itemsize, dtype=self.dtype)
+            ctx.d2h(raw.ctypes.data_as(C.c_void_p), self._block.ptr, raw.nbytes)
+            ctx.synchronize()
         v = np.lib.stride_tricks.as_strided(raw[self._offset:] if self._offset >= 0 else raw, shape=self._dims,
                                             strides=[s * self.dtype.itemsize for s in self._strides])
         if self._offset < 0:

@@ -124,3 +124,22 @@ def test_not_fused_when_the_consumer_sums_or_the_multiplier_comes_later(tb, orac
     # ... and computed before it: fused
     got = _run(tb, "ij,jk,il,lk->ik", arrays, [(2, 3), (0, 1), (5, 4)])
     assert oracle.rel_frobenius(got, oracle.np_einsum("ij,jk,il,lk->ik", arrays)) <= 1e-12
+
+
+@pytest.mark.parametrize("dtype", ALL_DTYPES)
+def test_summed_labels_of_extent_one_take_the_unfused_path(tb, oracle, dtype):
+    """A summed label of extent 1 vanishes when the modes are fused, so the product has nothing to
+    sum and cannot carry a multiplier: such a tree must run (unfused) and give the same result."""
+    rng = np.random.default_rng(95)
+    # j = 1: 'ij,jk' is an outer product
+    arrays = [random_array(rng, s, dtype) for s in ((60, 1), (1, 70), (60, 70))]
+    got = _run(tb, "ij,jk,ik->ik", arrays, [(0, 1), (2, 3)])
+    assert oracle.rel_frobenius(got, oracle.np_einsum("ij,jk,ik->ik", arrays)) <= TOL[np.dtype(dtype)]
+    # batched product whose every summed label has extent 1
+    arrays = [random_array(rng, s, dtype) for s in ((3, 40, 1, 1), (3, 1, 1, 50), (3, 40, 50))]
+    got = _run(tb, "bijl,bjlk,bik->bik", arrays, [(0, 1), (2, 3)])
+    assert oracle.rel_frobenius(got, oracle.np_einsum("bijl,bjlk,bik->bik", arrays)) <= TOL[np.dtype(dtype)]
+    # one summed label of extent 1 beside a real one: still fused, still right
+    arrays = [random_array(rng, s, dtype) for s in ((40, 1, 30), (1, 30, 50), (40, 50))]
+    got = _run(tb, "ijl,jlk,ik->ik", arrays, [(0, 1), (2, 3)])
+    assert oracle.rel_frobenius(got, oracle.np_einsum("ijl,jlk,ik->ik", arrays)) <= TOL[np.dtype(dtype)]
