@@ -34,6 +34,58 @@ def test_binding_table_matches_header(tb):
     assert sorted(_lib.PROTOTYPES) == header_symbols()
 
 
+def header_arity():
+    """{symbol: number of parameters} from the header's prototypes."""
+    text = (ROOT / "include" / "tenferro_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    out = {}
+    for name, params in re.findall(r"\b(tfb_[a-z0-9_]+)\s*\(([^()]*)\)\s*;", text):
+        params = params.strip()
+        out[name] = 0 if params in ("", "void") else len(params.split(","))
+    return out
+
+
+def test_rust_sys_crate_matches_the_header():
+    """The Rust `extern "C"` block is generated from the header and must agree with it: same
+    symbols, same number of parameters, and the committed file is what the generator writes now."""
+    import subprocess
+    import sys
+
+    sys_dir = ROOT / "rust" / "tenferro-b200-sys"
+    r = subprocess.run([sys.executable, str(sys_dir / "gen_sys.py"), "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    rs = (sys_dir / "src" / "lib.rs").read_text()
+    block = rs[rs.index('extern "C" {'):]
+    rust = {}
+    for name, params in re.findall(r"pub fn (tfb_[a-z0-9_]+)\(([^)]*)\)", block):
+        rust[name] = len([p for p in params.split(",") if p.strip()])
+    assert rust == header_arity()
+    # every enum constant and struct of the header is there too
+    text = (ROOT / "include" / "tenferro_b200.h").read_text()
+    for const in set(re.findall(r"\b(TFB_[A-Z0-9_]+)\b\s*(?:=|,|\})", re.sub(r"/\*.*?\*/", "", text, flags=re.S))):
+        assert f"pub const {const}:" in rs, const
+    for struct in ("tfb_desc", "tfb_view", "tfb_compute_device", "tfb_gemm_problem"):
+        assert f"pub struct {struct} {{" in rs
+    # field order and count of the view struct (the one every call passes)
+    view = rs[rs.index("pub struct tfb_view {"):]
+    fields = re.findall(r"pub (\w+):", view[:view.index("}")])
+    assert fields == ["base", "rank", "dims", "strides", "offset", "flags"]
+
+
+def test_rust_safe_crate_uses_only_declared_items():
+    """Every `sys::` item the safe crate names exists in the generated sys crate."""
+    rs = (ROOT / "rust" / "tenferro-b200-sys" / "src" / "lib.rs").read_text()
+    declared = set(re.findall(r"pub (?:fn|const|type|struct) (\w+)", rs))
+    used = set()
+    for path in (ROOT / "rust" / "tenferro-b200" / "src").glob("*.rs"):
+        used |= set(re.findall(r"\bsys::(\w+)", path.read_text()))
+    assert used and not (used - declared), sorted(used - declared)
+    # the four pieces the binding consists of
+    backend = (ROOT / "rust" / "tenferro-b200" / "src" / "backend.rs").read_text()
+    assert "impl TensorPrims<Standard> for CudaBackend" in backend
+    assert "impl<T: ScalarBase> Drop for CudaBuffer<T>" in (ROOT / "rust" / "tenferro-b200" / "src" / "buffer.rs").read_text()
+
+
 def test_version_and_device_format(tb):
     from tenferro_b200._lib import lib
 

@@ -59,3 +59,18 @@ def test_static_reduce_rejects_large_outputs(tb):
         reduce_static([0, 1], a, [0], out)
     with pytest.raises(tb.InvalidArgument):
         reduce_static([0, 0], tb.Tensor.zeros((4, 4)), [0], tb.Tensor.zeros((4,)))
+
+
+def test_static_reduce_empty_range_matches_the_plan(tb):
+    """A reduced mode of extent 0: the sum over nothing is 0, so both entry points leave beta * C."""
+    from tenferro_b200.prims import reduce_static
+
+    c0 = np.arange(6, dtype=np.float64)
+    a = tb.Tensor.zeros((6, 0), dtype=np.float64)
+    ref, got = tb.Tensor.from_numpy(c0), tb.Tensor.from_numpy(c0)
+    plan = tb.CudaBackend.plan(tb.PrimDescriptor.Reduce([0, 1], [0], tb.ReduceOp.Sum), [(6, 0), (6,)], np.float64)
+    tb.CudaBackend.execute(plan, 2.0, [a], -0.5, ref)
+    reduce_static([0, 1], a, [0], got, tb.ReduceOp.Sum, 2.0, -0.5)
+    assert np.array_equal(ref.to_numpy(), -0.5 * c0) and np.array_equal(got.to_numpy(), ref.to_numpy())
+    with pytest.raises(tb.InvalidArgument):
+        reduce_static([0, 1], a, [0], got, tb.ReduceOp.Max)
