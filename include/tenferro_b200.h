@@ -76,6 +76,13 @@ typedef enum tfb_reduce_op { TFB_REDUCE_SUM = 0, TFB_REDUCE_MAX = 1, TFB_REDUCE_
 /* Extension (tenferro-prims/src/lib.rs:123-128). */
 typedef enum tfb_extension { TFB_EXT_CONTRACT = 0, TFB_EXT_ELEMENTWISE_MUL = 1 } tfb_extension;
 
+/* The algebra `TensorPrims<A>` is parameterised by (tenferro-prims/src/lib.rs:278-280): a semiring
+ * {zero, one, add, mul} (tenferro-algebra/src/lib.rs:74-106).  Standard is (+, *) on f32, f64,
+ * Complex32, Complex64 (:56-72).  MaxPlus (the tropical semiring named at :81-90: add = max,
+ * mul = +, zero = -inf, one = 0) and its mirror MinPlus (add = min, zero = +inf) exist for f32
+ * and f64. */
+typedef enum tfb_algebra { TFB_ALGEBRA_STANDARD = 0, TFB_ALGEBRA_MAX_PLUS = 1, TFB_ALGEBRA_MIN_PLUS = 2 } tfb_algebra;
+
 /* OpKind (tenferro-device/src/lib.rs:77-90). */
 typedef enum tfb_op_kind {
     TFB_KIND_CONTRACT = 0,
@@ -273,6 +280,18 @@ const char* tfb_plan_kernel_name(const tfb_plan* plan);
  * environment variable TFB_C64_FOUR_PRODUCTS=1 for every Complex64 product including those of
  * an einsum tree, computes Re and Im each to its own accuracy at roughly 3/4 of the speed. */
 tfb_status tfb_plan_force_kernel(tfb_plan* plan, int kernel);
+
+/* `impl TensorPrims<A> for CudaBackend` with A other than Standard: the plan computes over
+ * semiring `algebra`,
+ *   output = alpha (x) op(inputs) (+) beta (x) output,
+ * with every sum of `op` taken with (+) and every product with (x).  For MaxPlus:
+ * C[m,n] = max(alpha + max_k(A[m,k] + B[k,n]), beta + C[m,n]); beta = -inf (the semiring's zero)
+ * overwrites C without reading it, alpha = 0 (its one) leaves the result as it is.  Tropical
+ * plans run on the SIMT kernels (tensor cores only multiply and add); AntiTrace and AntiDiag
+ * and the einsum tree executor are Standard-only. */
+tfb_status tfb_plan_set_algebra(tfb_plan* plan, int32_t algebra);
+/* has_extension_for::<T>(ext) of the backend for algebra A (tenferro-prims/src/lib.rs:322-339). */
+int tfb_has_extension_for_algebra(int32_t algebra, int32_t dtype, int32_t ext);
 
 /* TensorPrims::execute (tenferro-prims/src/lib.rs:300-320):
  *   output = alpha * op(inputs) + beta * output

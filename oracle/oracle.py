@@ -230,6 +230,38 @@ def np_elementwise_mul(a, b, alpha=1.0, beta=0.0, out_old=None):
 # ---------------------------------------------------------------------------------------
 # einsum
 # ---------------------------------------------------------------------------------------
+def np_semiring_contract(labels_in, operands, labels_out, algebra: int, alpha=None, beta=None, out_old=None):
+    """Contraction over a tropical semiring (tenferro-algebra/src/lib.rs:74-106: zero, one, add, mul;
+    MaxPlus at :81-90).  algebra 1 = MaxPlus (add = max, mul = +, zero = -inf, one = 0), 2 = MinPlus.
+        out = alpha (x) (+)_{labels not in the output} (x)_t operands[t]   (+)   beta (x) out_old
+    evaluated by broadcasting every operand to the full index space (small cases only)."""
+    red = np.max if algebra == 1 else np.min
+    pick = np.maximum if algebra == 1 else np.minimum
+    zero = -np.inf if algebra == 1 else np.inf
+    all_labels = list(labels_out) + sorted({l for ls in labels_in for l in ls} - set(labels_out))
+    ext = {}
+    for ls, op in zip(labels_in, operands):
+        for l, e in zip(ls, op.shape):
+            ext[l] = e
+    total = np.zeros([ext[l] for l in all_labels], dtype=np.float64)
+    for ls, op in zip(labels_in, operands):
+        # diagonal of repeated labels first, then broadcast into the full space
+        uniq = []
+        for l in ls:
+            if l not in uniq:
+                uniq.append(l)
+        sub = np.einsum(op.astype(np.float64), list(ls), uniq)
+        shape = [ext[l] if l in uniq else 1 for l in all_labels]
+        total = total + np.transpose(sub, [uniq.index(l) for l in all_labels if l in uniq]).reshape(shape)
+    n_out = len(labels_out)
+    value = red(total.reshape(total.shape[:n_out] + (-1,)), axis=-1) if total.ndim > n_out else total
+    if alpha is not None:
+        value = value + alpha
+    if beta is not None and beta != zero and out_old is not None:
+        value = pick(value, out_old.astype(np.float64) + beta)
+    return value
+
+
 def parse_notation(notation: str) -> Tuple[List[List[int]], List[int]]:
     """Labels of "ij,(jk,kl)->il" with a-z -> 0..25, A-Z -> 26..51
     (tenferro-einsum/src/lib.rs:260-283).  Parentheses only order the work, so they drop out."""

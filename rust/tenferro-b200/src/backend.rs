@@ -74,6 +74,18 @@ impl<T: ScalarBase> Drop for CudaPlan<T> {
     }
 }
 
+impl<T: ScalarBase> CudaPlan<T> {
+    /// Compute over another semiring (`sys::TFB_ALGEBRA_MAX_PLUS`, `sys::TFB_ALGEBRA_MIN_PLUS`; f32
+    /// and f64): what an external `impl TensorPrims<MaxPlus> for CudaBackend`
+    /// (`tenferro-algebra/src/lib.rs:12-16, 74-106`) calls after `plan` - the descriptor, shapes and
+    /// views are those of the Standard plan, only the arithmetic changes.
+    pub fn set_algebra(self, algebra: sys::tfb_algebra) -> Result<Self> {
+        // SAFETY: live plan handle, plain integer.
+        check(unsafe { sys::tfb_plan_set_algebra(self.raw, algebra) })?;
+        Ok(self)
+    }
+}
+
 /// The CUDA backend.  Associated functions only, like `CpuBackend`; the device is the current
 /// default (`CudaBackend::set_default_device`), device 0 unless changed.
 pub struct CudaBackend;

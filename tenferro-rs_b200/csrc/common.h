@@ -182,6 +182,8 @@ tfb_status launch_contract(tfb_ctx* ctx, const ContractProblem& p, int force_ker
 
 // Family-specific launchers (each may decline with *declined = true and TFB_OK).
 tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p);
+// Over a tropical semiring (tfb_algebra: 1 MaxPlus, 2 MinPlus); an empty K group is a single term.
+tfb_status contract_simt_semiring(tfb_ctx* ctx, const ContractProblem& p, int algebra);
 tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined, bool four_products = false);
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined,
                             const int64_t* const* c_tables = nullptr, const std::vector<Mode>* c_n_modes = nullptr,

@@ -221,8 +221,11 @@ void fill_args(const ContractProblem& p, const ContractTables& t, ContractArgs* 
 // 64 x 64 block tile, 16-deep k slices, 256 threads, 4 x 4 outputs per thread.  Exact in
 // the element type (FMA), any strides, any dtype.  It is the path of last resort: the
 // tensor-core kernels decline only layouts they cannot stage.
-template <typename T>
+// ALG selects the semiring (scalar_ops.cuh): the same loop nest computes
+// C = alpha (x) (+)_k A (x) B  (+)  beta (x) C for MaxPlus and MinPlus, which have no tensor-core form.
+template <typename T, int ALG = 0>
 __global__ void __launch_bounds__(256) contract_simt_kernel(ContractArgs g) {
+    using S = Semi<T, ALG>;
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ T As[BK][BM + 1];
     __shared__ T Bs[BK][BN + 1];
@@ -243,7 +246,7 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(ContractArgs g) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = Ops<T>::zero();
+            for (int j = 0; j < 4; ++j) acc[i][j] = S::zero();
         for (int64_t k0 = 0; k0 < g.K; k0 += BK) {
             // Gather the two operand slices; neighbouring threads follow the unit stride.
 #pragma unroll
@@ -251,13 +254,13 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(ContractArgs g) {
                 int c = tid + r * 256;
                 int mm, kk;
                 if (g.a_kfast) { kk = c % BK; mm = c / BK; } else { mm = c % BM; kk = c / BM; }
-                T v = Ops<T>::zero();
+                T v = S::zero();
                 if (m0 + mm < g.M && k0 + kk < g.K) v = Ab[g.a_m[m0 + mm] + g.a_k[k0 + kk]];
                 if (g.conj_a) v = Ops<T>::conj(v);
                 As[kk][mm] = v;
                 int nn;
                 if (g.b_kfast) { kk = c % BK; nn = c / BK; } else { nn = c % BN; kk = c / BN; }
-                T w = Ops<T>::zero();
+                T w = S::zero();
                 if (n0 + nn < g.N && k0 + kk < g.K) w = Bb[g.b_n[n0 + nn] + g.b_k[k0 + kk]];
                 if (g.conj_b) w = Ops<T>::conj(w);
                 Bs[kk][nn] = w;
@@ -273,13 +276,14 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(ContractArgs g) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[i][j] = Ops<T>::fma_(av[i], bv[j], acc[i][j]);
+                    for (int j = 0; j < 4; ++j) acc[i][j] = S::fma_(av[i], bv[j], acc[i][j]);
             }
             __syncthreads();
         }
         const T alpha = Ops<T>::from(Scalar{g.alpha_re, g.alpha_im});
         const T beta = Ops<T>::from(Scalar{g.beta_re, g.beta_im});
-        const bool read_c = g.beta_re != 0 || g.beta_im != 0;
+        // beta equal to the semiring's zero means "overwrite": the output is never read
+        const bool read_c = ALG == 0 ? (g.beta_re != 0 || g.beta_im != 0) : !(g.beta_re == (ALG == 1 ? -INFINITY : INFINITY));
         T* Cb = C + g.c_b[bb];
         const T* D = g.mul ? reinterpret_cast<const T*>(g.mul) + g.d_b[bb] : nullptr;
 #pragma unroll
@@ -297,8 +301,8 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(ContractArgs g) {
                     const T d = D[g.d_m[m] + g.d_n[n]];
                     sum = Ops<T>::mul(sum, g.conj_mul ? Ops<T>::conj(d) : d);
                 }
-                T v = Ops<T>::mul(alpha, sum);
-                if (read_c) v = Ops<T>::add(v, Ops<T>::mul(beta, *p));
+                T v = S::mul(alpha, sum);
+                if (read_c) v = S::add(v, S::mul(beta, *p));
                 *p = v;
             }
         }
@@ -323,6 +327,31 @@ tfb_status contract_simt(tfb_ctx* ctx, const ContractProblem& p) {
         case TFB_C64: contract_simt_kernel<double2><<<grid, 256, 0, ctx->stream>>>(a); break;
         default: return fail(TFB_ERR_INVALID_ARGUMENT, "unknown dtype %d", p.dtype);
     }
+    TFB_CUDA(cudaGetLastError());
+    return TFB_OK;
+}
+
+// The same kernel over a non-Standard semiring (real types only): 1 MaxPlus, 2 MinPlus.
+tfb_status contract_simt_semiring(tfb_ctx* ctx, const ContractProblem& p, int algebra) {
+    if (p.dtype != TFB_F32 && p.dtype != TFB_F64)
+        return fail(TFB_ERR_INVALID_ARGUMENT, "MaxPlus and MinPlus are defined for f32 and f64");
+    if (p.mul) return fail(TFB_ERR_INVALID_ARGUMENT, "a fused multiplier is a Standard-algebra feature");
+    DeviceGuard guard(ctx->device);
+    std::shared_ptr<ContractTables> t;
+    TFB_TRY(get_tables(ctx, p, &t));
+    ContractArgs a;
+    fill_args(p, *t, &a);
+    a.tiles_m = (a.M + 63) / 64;
+    a.tiles_n = (a.N + 63) / 64;
+    a.n_tiles = a.tiles_m * a.tiles_n * a.B;
+    if (a.n_tiles == 0) return TFB_OK;
+    int grid = (int)std::min<int64_t>(a.n_tiles, (int64_t)ctx->sm_count * 8);
+    LaunchScope ls(ctx, "contract_simt_semiring");
+    if (p.dtype == TFB_F32 && algebra == 1) contract_simt_kernel<float, 1><<<grid, 256, 0, ctx->stream>>>(a);
+    else if (p.dtype == TFB_F32 && algebra == 2) contract_simt_kernel<float, 2><<<grid, 256, 0, ctx->stream>>>(a);
+    else if (p.dtype == TFB_F64 && algebra == 1) contract_simt_kernel<double, 1><<<grid, 256, 0, ctx->stream>>>(a);
+    else if (p.dtype == TFB_F64 && algebra == 2) contract_simt_kernel<double, 2><<<grid, 256, 0, ctx->stream>>>(a);
+    else return fail(TFB_ERR_INVALID_ARGUMENT, "unknown algebra %d", algebra);
     TFB_CUDA(cudaGetLastError());
     return TFB_OK;
 }

@@ -176,7 +176,7 @@ tfb_status run_unary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& label
 tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labels_a, const HView& a,
                       const std::vector<uint32_t>& labels_b, const HView& b, const std::vector<uint32_t>& labels_c,
                       const HView& c, Scalar alpha, Scalar beta, int force_kernel, const char** used,
-                      const std::vector<uint32_t>* labels_d, const HView* d) {
+                      const std::vector<uint32_t>* labels_d, const HView* d, int algebra) {
     Labelled la, lb, lc, ld;
     bool ra = false, rb = false, rc = false, rd = false;
     TFB_TRY(merge_repeats(labels_a, a, &la, &ra, "first input"));
@@ -189,6 +189,10 @@ tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labe
                 return fail(TFB_ERR_INVALID_ARGUMENT, "a fused multiplier may only carry labels of a plain output");
     }
     if (c.conj) return fail(TFB_ERR_INVALID_ARGUMENT, "the output view cannot carry the conjugate flag");
+    if (algebra != TFB_ALGEBRA_STANDARD && (rc || d))
+        return fail(TFB_ERR_INVALID_ARGUMENT,
+                    "repeated output labels (AntiTrace, AntiDiag) and fused multipliers are implemented for the Standard "
+                    "algebra only");
     if (rc) {
         LoopNest all;
         TFB_TRY(full_nest_of(c, &all));
@@ -260,6 +264,12 @@ tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labe
     sort_and_fuse(p.m, 0, 4);
     sort_and_fuse(p.n, 1, 4);
     sort_and_fuse(p.k, 0, 4);
+    if (algebra != TFB_ALGEBRA_STANDARD) {
+        // Tropical semirings have no tensor-core form: every shape, with or without summed labels,
+        // runs on the SIMT kernel instantiated for the algebra.
+        if (used) *used = "simt_semiring";
+        return contract_simt_semiring(ctx, p, algebra);
+    }
     if (p.k.empty()) {
         if (d) return fail(TFB_ERR_INVALID_ARGUMENT, "a fused multiplier needs a product with summed labels");
         // No summation: C[b,m,n] = alpha * A[b,m] * B[b,n] + beta * C is element-wise with
@@ -538,7 +548,25 @@ tfb_status tfb_execute(tfb_plan* plan, const void* alpha, size_t n_inputs, const
         TFB_TRY(to_hview(inputs[1], plan->dtype, &vb, "second input"));
         TFB_TRY(to_hview(*output, plan->dtype, &vc, "output"));
         st = run_binary(plan->ctx, plan->dtype, plan->la, va, plan->lb, vb, plan->lc, vc, a, b, plan->force_kernel,
-                        &used);
+                        &used, nullptr, nullptr, plan->algebra);
+    } else if (plan->algebra != TFB_ALGEBRA_STANDARD) {
+        // One input over a tropical semiring: the same contraction with the semiring's ONE as the
+        // second operand - a single element without labels.  One is 0.0 in MaxPlus and MinPlus,
+        // i.e. all bits zero.  Reduce(Sum) becomes a maximum (minimum) over the reduced modes,
+        // Permute and Trace their semiring forms; alpha and beta combine by (x) = + and (+) = max.
+        if (plan->op == TFB_OP_REDUCE && plan->reduce_op != TFB_REDUCE_SUM)
+            return fail(TFB_ERR_INVALID_ARGUMENT, "over MaxPlus/MinPlus a Reduce sums with the algebra's own addition: use ReduceOp::Sum");
+        TFB_TRY(check_view_shape(inputs[0], plan->shapes[0], "input"));
+        TFB_TRY(check_view_shape(*output, plan->shapes[1], "output"));
+        HView vi, vo, one;
+        TFB_TRY(to_hview(inputs[0], plan->dtype, &vi, "input"));
+        TFB_TRY(to_hview(*output, plan->dtype, &vo, "output"));
+        PoolBlock unit;
+        TFB_TRY(unit.alloc(plan->ctx, 16));
+        TFB_CUDA(cudaMemsetAsync(unit.ptr, 0, 16, plan->ctx->stream));
+        one.ptr = (char*)unit.ptr;
+        st = run_binary(plan->ctx, plan->dtype, plan->la, vi, {}, one, plan->lc, vo, a, b, 0, &used, nullptr, nullptr,
+                        plan->algebra);
     } else {
         TFB_TRY(check_view_shape(inputs[0], plan->shapes[0], "input"));
         TFB_TRY(check_view_shape(*output, plan->shapes[1], "output"));
@@ -549,6 +577,27 @@ tfb_status tfb_execute(tfb_plan* plan, const void* alpha, size_t n_inputs, const
     }
     plan->kernel_name = used;
     return st;
+}
+
+tfb_status tfb_plan_set_algebra(tfb_plan* plan, int32_t algebra) {
+    if (!plan) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_plan_set_algebra: plan is NULL");
+    if (algebra < TFB_ALGEBRA_STANDARD || algebra > TFB_ALGEBRA_MIN_PLUS)
+        return fail(TFB_ERR_INVALID_ARGUMENT, "unknown algebra %d", (int)algebra);
+    if (algebra != TFB_ALGEBRA_STANDARD) {
+        if (plan->dtype != TFB_F32 && plan->dtype != TFB_F64)
+            return fail(TFB_ERR_INVALID_ARGUMENT, "MaxPlus and MinPlus are defined for f32 and f64");
+        if (plan->op == TFB_OP_ANTI_TRACE || plan->op == TFB_OP_ANTI_DIAG)
+            return fail(TFB_ERR_INVALID_ARGUMENT, "AntiTrace and AntiDiag are implemented for the Standard algebra only");
+    }
+    plan->algebra = algebra;
+    return TFB_OK;
+}
+
+int tfb_has_extension_for_algebra(int32_t algebra, int32_t dtype, int32_t ext) {
+    if (algebra == TFB_ALGEBRA_STANDARD) return tfb_has_extension(dtype, ext);
+    if (algebra != TFB_ALGEBRA_MAX_PLUS && algebra != TFB_ALGEBRA_MIN_PLUS) return 0;
+    if (dtype != TFB_F32 && dtype != TFB_F64) return 0;
+    return ext == TFB_EXT_CONTRACT || ext == TFB_EXT_ELEMENTWISE_MUL;
 }
 
 tfb_status tfb_plan_force_kernel(tfb_plan* plan, int kernel) {

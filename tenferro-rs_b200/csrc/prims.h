@@ -9,6 +9,7 @@ struct tfb_plan {
     bool binary = false;
     int reduce_op = TFB_REDUCE_SUM;
     int force_kernel = 0;  // tfb::ContractKernel
+    int algebra = 0;       // tfb_algebra
     std::vector<uint32_t> la, lb, lc;          // labels after lowering the descriptor
     std::vector<std::vector<int64_t>> shapes;  // inputs first, then output
     const char* kernel_name = "none";
@@ -25,6 +26,6 @@ tfb_status run_unary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& label
 tfb_status run_binary(tfb_ctx* ctx, int dtype, const std::vector<uint32_t>& labels_a, const HView& a,
                       const std::vector<uint32_t>& labels_b, const HView& b, const std::vector<uint32_t>& labels_c,
                       const HView& c, Scalar alpha, Scalar beta, int force_kernel, const char** used,
-                      const std::vector<uint32_t>* labels_d = nullptr, const HView* d = nullptr);
+                      const std::vector<uint32_t>* labels_d = nullptr, const HView* d = nullptr, int algebra = 0);
 
 }  // namespace tfb

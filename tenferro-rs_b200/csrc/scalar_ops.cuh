@@ -98,6 +98,32 @@ struct Ops<double2> {
     }
 };
 
+// Semirings (tenferro-algebra/src/lib.rs:74-106: zero, one, add, mul).  ALG 0 is the Standard
+// algebra (+, *) of all four element types; ALG 1 is MaxPlus (add = max, mul = +, zero = -inf,
+// one = 0) and ALG 2 MinPlus (add = min, zero = +inf), both for the real types.  `fma_(a, b, c)`
+// is c (+) a (x) b, the step of a contraction's inner loop.
+template <typename T, int ALG>
+struct Semi {
+    __device__ static T zero() { return Ops<T>::zero(); }
+    __device__ static T add(T a, T b) { return Ops<T>::add(a, b); }
+    __device__ static T mul(T a, T b) { return Ops<T>::mul(a, b); }
+    __device__ static T fma_(T a, T b, T c) { return Ops<T>::fma_(a, b, c); }
+};
+template <typename T>
+struct Semi<T, 1> {
+    __device__ static T zero() { return Ops<T>::lowest(); }
+    __device__ static T add(T a, T b) { return Ops<T>::max_(a, b); }
+    __device__ static T mul(T a, T b) { return a + b; }
+    __device__ static T fma_(T a, T b, T c) { return Ops<T>::max_(c, a + b); }
+};
+template <typename T>
+struct Semi<T, 2> {
+    __device__ static T zero() { return Ops<T>::highest(); }
+    __device__ static T add(T a, T b) { return Ops<T>::min_(a, b); }
+    __device__ static T mul(T a, T b) { return a + b; }
+    __device__ static T fma_(T a, T b, T c) { return Ops<T>::min_(c, a + b); }
+};
+
 // V elements moved as one access.
 template <typename T, int V>
 struct __align__(sizeof(T) * V) Pack {

@@ -34,6 +34,6 @@ from .einsum import (  # noqa: F401
     einsum_with_subscripts_owned,
 )
 from .prims import (  # noqa: F401
-    ContractKernel, CudaBackend, CudaPlan, Extension, PreparedGroupedGemm, PrimDescriptor, ReduceOp, grouped_gemm,
+    Algebra, ContractKernel, CudaBackend, CudaPlan, Extension, PreparedGroupedGemm, PrimDescriptor, ReduceOp, grouped_gemm,
 )
 from .tensor import MemoryOrder, Tensor  # noqa: F401

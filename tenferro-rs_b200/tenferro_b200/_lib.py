@@ -111,6 +111,8 @@ PROTOTYPES = {
     "tfb_plan_destroy": (C.c_int, [_VP]),
     "tfb_plan_kernel_name": (C.c_char_p, [_VP]),
     "tfb_plan_force_kernel": (C.c_int, [_VP, C.c_int]),
+    "tfb_plan_set_algebra": (C.c_int, [_VP, C.c_int32]),
+    "tfb_has_extension_for_algebra": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
     "tfb_execute": (C.c_int, [_VP, _VP, C.c_size_t, C.POINTER(TfbView), _VP, C.POINTER(TfbView)]),
     "tfb_reduce_static": (
         C.c_int, [_VP, C.c_int32, C.c_int32, c_u32_p, C.c_size_t, C.POINTER(TfbView), c_u32_p, C.c_size_t,

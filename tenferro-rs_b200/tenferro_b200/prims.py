@@ -40,6 +40,15 @@ class ContractKernel(enum.IntEnum):
     Dmma4 = 4  # Complex64 with four real products per complex one: Re and Im each to their own accuracy
 
 
+class Algebra(enum.IntEnum):
+    """The algebra parameter A of `TensorPrims<A>` (tenferro-algebra/src/lib.rs:56, 74-106).
+    Standard: (+, *).  MaxPlus: add = max, mul = +, zero = -inf, one = 0.  MinPlus: its mirror."""
+
+    Standard = 0
+    MaxPlus = 1
+    MinPlus = 2
+
+
 _OPS = {"BatchedGemm": 0, "Reduce": 1, "Trace": 2, "Permute": 3, "AntiTrace": 4, "AntiDiag": 5, "Contract": 6,
         "ElementwiseMul": 7}
 
@@ -123,6 +132,11 @@ class CudaPlan:
         self.desc = desc
         self.ctx = ctx
 
+    def set_algebra(self, algebra: Algebra) -> "CudaPlan":
+        """Compute over another semiring: output = alpha (x) op(inputs) (+) beta (x) output."""
+        check(lib.tfb_plan_set_algebra(self.handle, int(algebra)))
+        return self
+
     def force_kernel(self, kernel: ContractKernel) -> "CudaPlan":
         check(lib.tfb_plan_force_kernel(self.handle, int(kernel)))
         return self
@@ -153,8 +167,9 @@ class CudaBackend:
 
     @staticmethod
     def plan(desc: PrimDescriptor, shapes: Sequence[Sequence[int]], dtype=np.float64,
-             ctx: Optional[Context] = None) -> CudaPlan:
-        """`plan::<T>(desc, shapes)`; shapes are inputs first, then the output."""
+             ctx: Optional[Context] = None, algebra: Algebra = Algebra.Standard) -> CudaPlan:
+        """`plan::<T>(desc, shapes)`; shapes are inputs first, then the output.  `algebra` is the A of
+        `impl TensorPrims<A> for CudaBackend`."""
         ctx = ctx or Context.get(0)
         keep: list = []
         cdesc = desc._to_c(keep)
@@ -164,7 +179,10 @@ class CudaBackend:
         dims = (_lib.c_size_p * max(n, 1))(*[C.cast(r, _lib.c_size_p) for r in rows])
         h = C.c_void_p()
         check(lib.tfb_plan_create(ctx.handle, C.byref(cdesc), dtype_code(dtype), n, ranks, dims, C.byref(h)))
-        return CudaPlan(h, dtype, desc, ctx)
+        plan = CudaPlan(h, dtype, desc, ctx)
+        if algebra != Algebra.Standard:
+            plan.set_algebra(algebra)
+        return plan
 
     @staticmethod
     def execute(plan: CudaPlan, alpha, inputs: Sequence[Tensor], beta, output: Tensor) -> None:
@@ -191,13 +209,13 @@ class CudaBackend:
         output.event = ctx.record_event()
 
     @staticmethod
-    def has_extension_for(dtype, ext: Extension) -> bool:
-        """`has_extension_for::<T>(ext)`."""
+    def has_extension_for(dtype, ext: Extension, algebra: Algebra = Algebra.Standard) -> bool:
+        """`has_extension_for::<T>(ext)` of the backend for `algebra`."""
         try:
             code = dtype_code(dtype)
         except InvalidArgument:
             return False
-        return bool(lib.tfb_has_extension(code, int(ext)))
+        return bool(lib.tfb_has_extension_for_algebra(int(algebra), code, int(ext)))
 
 
 class PreparedGroupedGemm:
