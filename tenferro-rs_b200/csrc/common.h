@@ -187,7 +187,8 @@ tfb_status contract_simt_semiring(tfb_ctx* ctx, const ContractProblem& p, int al
 tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined, bool four_products = false);
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined,
                             const int64_t* const* c_tables = nullptr, const std::vector<Mode>* c_n_modes = nullptr,
-                            int c_scale = 1);
+                            int c_scale = 1, const std::vector<Mode>* c_m_modes = nullptr,
+                            const std::vector<Mode>* c_batch_modes = nullptr);
 tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* declined);
 
 // Scratch from the context pool, released stream-ordered when the object dies.

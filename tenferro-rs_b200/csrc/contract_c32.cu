@@ -189,7 +189,7 @@ static tfb_status embedded_product(tfb_ctx* ctx, const ContractProblem& p, bool*
     q.k.push_back(Mode{2 * K, {1, 1, 0}});
     const int64_t* c_tables[3] = {tab_b, tab_m, tab_n};
     bool d = false;
-    TFB_TRY(contract_tcgen05(ctx, q, &d, c_tables, &p.n, 2));
+    TFB_TRY(contract_tcgen05(ctx, q, &d, c_tables, &p.n, 2, &p.m, &p.batch));
     if (d) return fail(TFB_ERR_DEVICE, "internal: the embedded real product was declined by the tensor-core kernel");
     *declined = false;
     return TFB_OK;

@@ -79,6 +79,12 @@ struct TcArgs {
     int k_split, kb_per_split;    // split-K: CTAs per output tile, k-blocks per CTA
     float* partial;               // split-K: [tile][split][BN cols][128 rows] raw sums
     int* status;
+    // Output through TMA tensor stores (CTA-pair kernel): finished sums are staged in shared memory,
+    // 32 rows x 32 columns per warp at a time, and leave as one bulk store each.  cm_e1: extent of
+    // the output's unit-stride row mode (rows of one run); row r of the M group has tensor-map
+    // coordinates (r % cm_e1, r / cm_e1), column n has (n % cn_e1, n / cn_e1).
+    int c_tma;
+    int cm_e1;
 };
 
 // First row (linear index in the group), valid rows and tensor-map coordinates of free-group tile `t`.
@@ -448,6 +454,10 @@ __global__ void __launch_bounds__(256) tf32x3_splitk_finish_kernel(TcArgs g) {
 // Arrivals on the leader's barriers from the other CTA go to the mapped address with CTA-scope
 // release semantics (see mbar_arrive_cluster); commits go to each CTA's barrier by an
 // instruction of its own, so every instruction here addresses exactly one CTA.
+// Output boxes of the TMA-store epilogue: 32 rows (one warp's TMEM lanes) x kBoxCols columns.
+constexpr int kBoxCols = 32;
+constexpr int kBoxBytes = 32 * kBoxCols * 4;
+
 struct PairCfg {
     static constexpr int BN = 256;                  // tile columns of the pair
     static constexpr int A_BYTES = kBM * kBK * 4;   // 16 KB: this CTA's 128 rows
@@ -455,11 +465,24 @@ struct PairCfg {
     static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);
     static constexpr int STAGES = 3;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+    // staging of output boxes for TMA stores: 8 warps x one 4 KB box (general kernel) or 4 drain
+    // warps x two boxes (short-K kernel)
+    static constexpr int OUT_STAGE_BYTES = 8 * kBoxBytes;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + OUT_STAGE_BYTES + 1024;
     static constexpr int TMEM_COLS = 2 * BN;
     static constexpr int COLS_PER_WARP = BN / 2;
     static_assert(kChunk >= STAGES, "promotion lag assumes a chunk spans at least the ring");
+    static_assert((STAGES * STAGE_BYTES + BAR_BYTES) % 128 == 0, "the output staging area must be 128-byte aligned");
 };
+
+// Finished columns [kBoxCols Q, kBoxCols (Q + 1)) of one thread's row, scaled, into the warp's
+// staging box (column-major: 32 rows of one column are 128 contiguous bytes, so the warp's stores
+// to shared memory are conflict-free and the box is what a {32, kBoxCols} TMA store expects).
+template <int Q, int N>
+__device__ __forceinline__ void stage_acc_cols(const float (&acc)[N], float* box_lane, float alpha) {
+#pragma unroll
+    for (int jj = 0; jj < kBoxCols; ++jj) box_lane[jj * 32] = alpha * acc[kBoxCols * Q + jj];
+}
 
 // Columns [Q, Q + 1) * ceil(N / SLICES) of one thread's row of finished sums.  Column offsets
 // follow the (at most two) output modes of the N side in closed form - no table loads in the
@@ -554,8 +577,11 @@ __device__ __forceinline__ int pair_num_kb(const TcArgs& g, int64_t w) {
 // wait for the memory system no longer hold up the conversion the tensor cores are waiting for:
 // a short-K product writes its output at DRAM speed WHILE the next tiles are multiplied.
 template <bool MUL, bool SHORTK>
+// (Ten warps sit three to a scheduler partition of 16 K registers: 168 registers per thread is the
+// most the launch bounds allow, and what the general instantiations use.)
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + kSplitThreads, 1)
-contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
+contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            const __grid_constant__ CUtensorMap map_c, TcArgs g) {
     using Cfg = PairCfg;
     constexpr int STAGES = Cfg::STAGES, BN = Cfg::BN, CPW = Cfg::COLS_PER_WARP;
     extern __shared__ char smem_raw[];
@@ -572,6 +598,9 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     auto bar_promoted = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
     const uint32_t tmem_word = bars + 8u * (3 * STAGES + 4);
     volatile uint32_t* tmem_word_ptr = (volatile uint32_t*)(smem + STAGES * Cfg::STAGE_BYTES + 8 * (3 * STAGES + 4));
+    // staging area of the TMA-store epilogue (see PairCfg::OUT_STAGE_BYTES)
+    const uint32_t out_stage = bars + Cfg::BAR_BYTES;
+    float* out_stage_ptr = (float*)(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -745,6 +774,9 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int row = lane_grp * 32 + lane;
             const uint32_t tmem_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
             const bool read_c = g.beta != 0.f;
+            // TMA-store path: two 2 KB boxes per drain warp, used alternately
+            const int slot0 = (warp - 2 - kRoleWarps) * 2;
+            uint32_t n_boxes = 0;
             uint32_t chunk = 0;
             for (int64_t w = w0; w < n_work; w += wstep, ++chunk) {
                 const PairWork pw = pair_work(g, w, rank);
@@ -753,6 +785,47 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 __syncwarp();
                 tc_fence_after();
                 const bool live = row < pw.tr_m.valid;
+                if (!MUL && g.c_tma) {
+                    static_assert(kBoxCols == 32, "boxes are read from tensor memory with one 32-column load");
+                    // 32 rows x 32 columns at a time: tcgen05.ld -> registers -> shared memory -> one bulk
+                    // tensor store.  The warp's global stores no longer sit in the load/store queue that
+                    // the converter warps' shared-memory traffic goes through, and the read of the next
+                    // box is in flight while this one is staged.
+                    const bool rows_live = 32 * lane_grp < pw.tr_m.valid;  // warp-uniform
+                    const int row_lin = (int)pw.tr_m.base + 32 * lane_grp;
+                    const int m_in = row_lin % g.cm_e1, m_out = row_lin / g.cm_e1;
+                    // box b of the tile: half b / 4, columns 32 (b % 4) .. + 31 of it
+                    auto box_valid = [&](int b) { return rows_live && pw.tr_n[b >> 2].valid > (b & 3) * 32; };
+                    auto box_taddr = [&](int b) { return tmem_row + (uint32_t)(buf * BN + b * 32); };
+                    uint32_t r[2][32];
+                    if (box_valid(0)) tc_ld32(box_taddr(0), r[0]);
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {
+                        if (!box_valid(b)) continue;
+                        tc_wait_ld();
+                        if (b + 1 < 8 && box_valid(b + 1)) tc_ld32(box_taddr(b + 1), r[(b + 1) & 1]);
+                        const int slot = slot0 + (int)(n_boxes & 1u);
+                        if (lane == 0) bulk_wait_read<1>();  // the box written two stores ago has been read
+                        __syncwarp();
+                        float* box = out_stage_ptr + slot * (kBoxBytes / 4) + lane;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) box[j * 32] = g.alpha * __uint_as_float(r[b & 1][j]);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const TileRows trn = pw.tr_n[b >> 2];
+                            const int col = (int)trn.base + (b & 3) * 32;
+                            tma_store_5d(&map_c, out_stage + (uint32_t)(slot * kBoxBytes), m_in, m_out, col % g.cn_e1, col / g.cn_e1,
+                                         (int)pw.batch);
+                            bulk_commit();
+                        }
+                        ++n_boxes;
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(leader_promoted0 + 8u * buf);
+                    continue;
+                }
                 float* C = reinterpret_cast<float*>(g.c);
                 if (live) C += g.c_b[pw.batch] + g.c_m[pw.tr_m.base + row];
                 const float* D = g.mul;  // fused multiplier's row (MUL only)
@@ -811,6 +884,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(leader_promoted0 + 8u * buf);
             }
+            if (lane == 0) bulk_wait<0>();  // every bulk store of this warp has been performed
         }
     } else {
         // ---------------------------------------------------------------- split + promote, then epilogue
@@ -828,11 +902,36 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // next tile's first k-blocks (its first promotion, which needs `acc` cleared, comes
         // later); what is left is flushed before that promotion.
         constexpr int kSlices = 6;
+        // With the TMA-store epilogue the pending tile leaves in kTmaSlices boxes of kBoxCols columns,
+        // staged in this warp's box of shared memory (warp - 2 = slot) and written by one bulk store each.
+        constexpr int kTmaSlices = CPW / kBoxCols;
+        const bool c_tma = !MUL && g.c_tma;
+        const int n_slices = c_tma ? kTmaSlices : kSlices;
+        float* const my_box = out_stage_ptr + (warp - 2) * (kBoxBytes / 4) + lane;
+        const uint32_t my_box_addr = out_stage + (uint32_t)((warp - 2) * kBoxBytes);
+        int pend_m_in = 0, pend_m_out = 0, pend_batch = 0;  // tensor-map coordinates of the pending tile's rows
         float* pend_row = nullptr;   // &C[row, 0] of the pending tile, nullptr: nothing pending
         const float* pend_drow = nullptr;  // the fused multiplier's row of that tile, nullptr: no multiplier
         int pend_col0 = 0;           // linear index of its first column
         int pend_valid = 0, pend_next = kSlices;
-        auto store_slice = [&](int sl) {
+        auto store_box = [&](int sl) {
+            if (kBoxCols * sl >= pend_valid) return;  // warp-uniform: these columns lie past the end
+            if (lane == 0) bulk_wait_read<0>();  // the previous box of this warp has been read
+            __syncwarp();
+            static_assert(kTmaSlices == 4, "the if-chain below names every box of a warp's columns");
+            if (sl == 0) stage_acc_cols<0, CPW>(acc, my_box, g.alpha);
+            else if (sl == 1) stage_acc_cols<1, CPW>(acc, my_box, g.alpha);
+            else if (sl == 2) stage_acc_cols<2, CPW>(acc, my_box, g.alpha);
+            else stage_acc_cols<3, CPW>(acc, my_box, g.alpha);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                const int col = pend_col0 + kBoxCols * sl;
+                tma_store_5d(&map_c, my_box_addr, pend_m_in, pend_m_out, col % g.cn_e1, col / g.cn_e1, pend_batch);
+                bulk_commit();
+            }
+        };
+        auto store_slice_scalar = [&](int sl) {
             // an if-chain on purpose: with a switch the compiler turns the slice number into an
             // index and moves `acc` to local memory
             if (sl == 0) store_acc_slice<0, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
@@ -842,12 +941,16 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             else if (sl == 4) store_acc_slice<4, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
             else store_acc_slice<5, kSlices, CPW, MUL>(acc, pend_row, pend_col0, g.cn_e1, g.cn_s1, g.cn_s2, pend_valid, g.alpha, g.beta, pend_drow, g.dn_s1, g.dn_s2);
         };
+        auto store_slice = [&](int sl) {
+            if (c_tma) store_box(sl);
+            else store_slice_scalar(sl);
+        };
         auto flush_pending = [&]() {
             if (pend_row) {
 #pragma unroll
                 for (int sl = 0; sl < kSlices; ++sl)
-                    if (sl >= pend_next) store_slice(sl);
-                pend_next = kSlices;
+                    if (sl >= pend_next && sl < n_slices) store_slice(sl);
+                pend_next = n_slices;
             }
             pend_row = nullptr;
         };
@@ -900,11 +1003,11 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // No promotion of this tile is due before k-block kChunk - 1 + STAGES: until then `acc`
         // still holds the previous tile, which leaves slice by slice.
         constexpr int kQuiet = kChunk - 1 + STAGES;
-        static_assert(kQuiet >= kSlices, "every slice gets a k-block of its own");
+        static_assert(kQuiet >= kSlices && kQuiet >= kTmaSlices, "every slice gets a k-block of its own");
         int kb = 0;
         for (; kb < num_kb && kb < kQuiet; ++kb) {
             convert_block();
-            if (pend_row && pend_next < kSlices) store_slice(pend_next++);
+            if (pend_row && pend_next < n_slices) store_slice(pend_next++);
         }
         flush_pending();
 #pragma unroll
@@ -926,6 +1029,18 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             float* P = g.partial + ((size_t)((pw.pair_tile * 2 + rank) * g.k_split + pw.split) * BN + col0) * kBM + row;
 #pragma unroll
             for (int j = 0; j < CPW; ++j) P[(size_t)j * kBM] = acc[j];
+        } else if (c_tma) {
+            // the warp's 32 rows x 128 columns leave as boxes during the next tile's first k-blocks
+            if (32 * lane_grp < tr_m.valid && trn.valid > 0) {
+                const int64_t row_lin = tr_m.base + 32 * lane_grp;
+                pend_row = reinterpret_cast<float*>(g.c);  // only marks "pending" on this path
+                pend_m_in = (int)(row_lin % g.cm_e1);
+                pend_m_out = (int)(row_lin / g.cm_e1);
+                pend_batch = (int)bb;
+                pend_col0 = (int)trn.base;
+                pend_valid = trn.valid;
+                pend_next = 0;
+            }
         } else if (row < tr_m.valid && trn.valid > 0) {
             float* C = reinterpret_cast<float*>(g.c) + g.c_b[bb] + g.c_m[tr_m.base + row];
             if (g.cn_e1 != 0) {
@@ -957,6 +1072,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
         }
         flush_pending();
+        if (c_tma && lane == 0) bulk_wait<0>();  // every bulk store of this warp has been performed
     }
     tc_fence_before();
     cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still reach into it
@@ -1141,6 +1257,47 @@ OperandMap make_operand_map(const ContractProblem& p, const std::vector<Mode>& f
     return out;
 }
 
+// The output as a rank-5 tensor [m1, m2, n1, n2, batch] for TMA stores of {32 rows, kBoxCols columns}
+// boxes.  `m` / `n` / `batch` are the output's M, N and batch modes in the order the kernel
+// linearises rows and columns (the operands' order), with the output's element strides in slot 2;
+// `scale` = 2 views a complex output as floats (the unit-stride row mode then holds interleaved
+// real and imaginary rows).  Fails (returns false) for layouts a tensor store cannot express; the
+// kernel then keeps its per-element stores.
+bool make_output_map(void* base, const std::vector<Mode>& m, const std::vector<Mode>& n, const std::vector<Mode>& batch,
+                     int scale, const TcGeom& ga, const TcGeom& gb, CUtensorMap* map, int* cm_e1) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc || m.empty() || n.empty() || m.size() > 2 || n.size() > 2 || batch.size() > 1) return false;
+    if ((uintptr_t)base % 16 != 0 || m[0].s[2] != 1) return false;
+    const int64_t e1 = scale * m[0].extent, e2 = m.size() == 2 ? m[1].extent : 1;
+    const int64_t s2 = m.size() == 2 ? scale * m[1].s[2] : 4;
+    const int64_t f1 = n[0].extent, f2 = n.size() == 2 ? n[1].extent : 1;
+    const int64_t t1 = scale * n[0].s[2], t2 = n.size() == 2 ? scale * n[1].s[2] : 4;
+    const int64_t B = batch.empty() ? 1 : batch[0].extent, bs = batch.empty() ? 4 : scale * batch[0].s[2];
+    auto aligned = [](int64_t extent, int64_t st) { return extent <= 1 || (st > 0 && st % 4 == 0); };
+    if (!aligned(e2, s2) || !aligned(f1, t1) || !aligned(f2, t2) || !aligned(B, bs)) return false;
+    // A warp's 32 rows (a box's columns) must lie inside one run of the unit-stride row mode (one run
+    // of the inner column mode): either the mode is the only one of its group, or the run length
+    // is a multiple of the box, or the kernel's tiles never cross a run (tiling inside the inner
+    // mode of a two-mode group, the same mode here).
+    const bool rows_ok = m.size() == 1 || e1 % 32 == 0 || (!ga.pack && ga.e1 == e1 && scale == 1);
+    const bool cols_ok = n.size() == 1 || f1 % kBoxCols == 0 || (!gb.pack && gb.e1 == f1);
+    if (!rows_ok || !cols_ok) return false;
+    if (e1 >= INT32_MAX || f1 >= INT32_MAX) return false;
+    auto stride_or_dummy = [](int64_t extent, int64_t st) -> cuuint64_t { return (cuuint64_t)(extent > 1 ? st : 4) * 4; };
+    cuuint64_t dims[5] = {(cuuint64_t)e1, (cuuint64_t)e2, (cuuint64_t)f1, (cuuint64_t)f2, (cuuint64_t)B};
+    cuuint64_t strides[4] = {stride_or_dummy(e2, s2), stride_or_dummy(f1, t1), stride_or_dummy(f2, t2), stride_or_dummy(B, bs)};
+    cuuint32_t box[5] = {32, 1, kBoxCols, 1, 1}, estr[5] = {1, 1, 1, 1, 1};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] % 16 != 0 || strides[i] >= (1ull << 40)) return false;
+    for (int i = 0; i < 5; ++i)
+        if (dims[i] == 0 || dims[i] > 0xffffffffull) return false;
+    if (enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    *cm_e1 = (int)e1;
+    return true;
+}
+
 // Split K when the tiles alone leave SMs idle: pick the split that minimises
 // (waves of CTAs) x (k-blocks per CTA + a fixed cost for prologue, epilogue and the finishing
 // pass), preferring fewer splits unless more of them save a tenth.  `slots` = tiles that run at once.
@@ -1215,7 +1372,7 @@ tfb_status launch_tc(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcA
     return TFB_OK;
 }
 
-tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, TcArgs g) {
+tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b, const CUtensorMap* c_map, TcArgs g) {
     using Cfg = PairCfg;
     static std::mutex mu;
     static std::map<int, bool> configured;
@@ -1254,19 +1411,22 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
         TFB_TRY(ws.alloc(ctx, (size_t)(2 * n_work) * Cfg::BN * kBM * sizeof(float)));
         g.partial = (float*)ws.ptr;
     }
+    // Split-K partials leave through the finishing kernel; a fused multiplier through the scalar path.
+    if (via_partials || g.mul || !c_map) g.c_tma = 0;
+    const CUtensorMap& mc = (g.c_tma && c_map) ? *c_map : a.map;  // unused when c_tma is off
     {
         LaunchScope ls(ctx, "contract_tf32x3");
         // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
         // short K, one accumulation chunk per tile: the variant with dedicated drain warps
         const bool short_k = !via_partials && g.num_kb <= kChunk && env_int("TFB_TC_SHORTK", 1);
         if (g.mul && short_k)
-            contract_tf32x3_pair_kernel<true, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+            contract_tf32x3_pair_kernel<true, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
         else if (g.mul)
-            contract_tf32x3_pair_kernel<true, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+            contract_tf32x3_pair_kernel<true, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
         else if (short_k)
-            contract_tf32x3_pair_kernel<false, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+            contract_tf32x3_pair_kernel<false, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
         else
-            contract_tf32x3_pair_kernel<false, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, g);
+            contract_tf32x3_pair_kernel<false, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
         TFB_CUDA(cudaGetLastError());
     }
     if (via_partials) {
@@ -1403,8 +1563,11 @@ extern "C" tfb_status tfb_probe_tf32_tflops_sustained(tfb_ctx* ctx, double secon
 // through its f32 view this way; `c_n_modes` / `c_scale` then describe the column offsets in closed form
 // (the N modes of the complex problem, strides times 2).
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined, const int64_t* const* c_tables,
-                            const std::vector<Mode>* c_n_modes, int c_scale) {
+                            const std::vector<Mode>* c_n_modes, int c_scale, const std::vector<Mode>* c_m_modes,
+                            const std::vector<Mode>* c_batch_modes) {
     const std::vector<Mode>* cn_modes = c_tables ? c_n_modes : &p.n;
+    const std::vector<Mode>* cm_modes = c_tables ? c_m_modes : &p.m;
+    const std::vector<Mode>* cb_modes = c_tables ? c_batch_modes : &p.batch;
     if (!c_tables) c_scale = 1;
     *declined = true;
     if (p.dtype != TFB_F32) return TFB_OK;
@@ -1506,7 +1669,19 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     g.num_kb = (int)((K / g.k_e1) * g.k_blocks1);
     g.status = ctx->dev_status;
     *declined = false;
-    if (pair) return launch_tc_pair(ctx, a, b, g);
+    // Output through TMA stores where the layout allows it and nothing of the old output is needed.
+    CUtensorMap c_map;
+    bool have_c_map = false;
+    if (pair && g.beta == 0.f && !p.mul && g.cn_e1 != 0 && cm_modes && cn_modes && cb_modes &&
+        env_int("TFB_TC_TMA_STORE", 1)) {
+        int cm_e1 = 0;
+        have_c_map = make_output_map(p.c, *cm_modes, *cn_modes, *cb_modes, c_scale, a.geom, b.geom, &c_map, &cm_e1);
+        if (have_c_map) {
+            g.c_tma = 1;
+            g.cm_e1 = cm_e1;
+        }
+    }
+    if (pair) return launch_tc_pair(ctx, a, b, have_c_map ? &c_map : nullptr, g);
     return bn == 256 ? launch_tc<256>(ctx, a, b, g) : launch_tc<128>(ctx, a, b, g);
 }
 
