@@ -798,12 +798,17 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     auto box_valid = [&](int b) { return rows_live && pw.tr_n[b >> 2].valid > (b & 3) * 32; };
                     auto box_taddr = [&](int b) { return tmem_row + (uint32_t)(buf * BN + b * 32); };
                     uint32_t r[2][32];
-                    if (box_valid(0)) tc_ld32(box_taddr(0), r[0]);
+                    bool in_flight = false;  // the read of box b was issued while box b - 1 was staged
 #pragma unroll
                     for (int b = 0; b < 8; ++b) {
-                        if (!box_valid(b)) continue;
+                        if (!box_valid(b)) {
+                            in_flight = false;
+                            continue;
+                        }
+                        if (!in_flight) tc_ld32(box_taddr(b), r[b & 1]);
                         tc_wait_ld();
-                        if (b + 1 < 8 && box_valid(b + 1)) tc_ld32(box_taddr(b + 1), r[(b + 1) & 1]);
+                        in_flight = b + 1 < 8 && box_valid(b + 1);
+                        if (in_flight) tc_ld32(box_taddr(b + 1), r[(b + 1) & 1]);
                         const int slot = slot0 + (int)(n_boxes & 1u);
                         if (lane == 0) bulk_wait_read<1>();  // the box written two stores ago has been read
                         __syncwarp();

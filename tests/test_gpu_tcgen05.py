@@ -212,3 +212,50 @@ def test_network_einsum_complex64_dim32(tb, oracle):
     ops = [oracle.normal(4000 + i, (32, 32, 32), np.complex64) for i in range(4)]
     got = tb.einsum("ijk,jlm,kmn,lnp->ip", [tb.Tensor.from_numpy(o) for o in ops]).to_numpy()
     assert oracle.rel_frobenius(got, oracle.np_einsum("ijk,jlm,kmn,lnp->ip", ops)) <= 1e-5
+
+
+def _einsum_both_store_paths(tb, monkeypatch, notation, ops, alpha=1.0):
+    """Run one einsum with the TMA-store epilogue on and off; returns the two results."""
+    outs = []
+    tree = tb.ContractionTree.optimize(tb.Subscripts.parse(notation), [o.dims() for o in ops])
+    for flag in ("1", "0"):
+        monkeypatch.setenv("TFB_TC_TMA_STORE", flag)
+        out = tb.Tensor.empty(tree.output_dims, ops[0].dtype)
+        tb.einsum_with_plan_into(tree, ops, alpha, 0.0, out)
+        outs.append(out.to_numpy())
+    return outs
+
+
+@pytest.mark.parametrize("k", [64, 1000], ids=["short-K drain warps", "general kernel"])
+def test_tma_store_epilogue_matches_per_element_stores(tb, oracle, monkeypatch, k):
+    """Outputs the CTA-pair kernel can describe as a tensor map leave through TMA tensor stores
+    (32 x 32 boxes staged in shared memory).  Same arithmetic, another way out: the results must be
+    bit-identical to the per-element store path, for ragged edges, two-mode row and column groups,
+    the float view of a complex output, and alpha != 1."""
+    rng = np.random.default_rng(500 + k)
+    T = tb.Tensor.from_numpy
+    space = tb.LogicalMemorySpace.GpuMemory(0)
+    # ragged single-mode rows and columns
+    a, b = random_array(rng, (300, k), np.float32), random_array(rng, (k, 520), np.float32)
+    on, off = _einsum_both_store_paths(tb, monkeypatch, "ij,jk->ik", [T(a), T(b)], alpha=0.5)
+    assert np.array_equal(on, off)
+    assert oracle.rel_frobenius(on, 0.5 * (a.astype(np.float64) @ b.astype(np.float64))) <= 1e-5
+    # two-mode rows (i = 64 of a pitch of 96, then j) and two-mode columns (m = 96 of a pitch of 128, then n)
+    kk = k // 4 * 4
+    a_full, b_full = random_array(rng, (96, 5, kk), np.float32), random_array(rng, (kk, 128, 7), np.float32)
+    ta, tb_ = T(a_full), T(b_full)
+    a_view = tb.Tensor(ta._block, (64, 5, kk), ta.strides(), 0, np.float32, space)
+    b_view = tb.Tensor(tb_._block, (kk, 96, 7), tb_.strides(), 0, np.float32, space)
+    on, off = _einsum_both_store_paths(tb, monkeypatch, "ijk,kmn->ijmn", [a_view, b_view])
+    want = np.einsum("ijk,kmn->ijmn", a_full[:64].astype(np.float64), b_full[:, :96].astype(np.float64))
+    assert np.array_equal(on, off)
+    assert oracle.rel_frobenius(on, want) <= 1e-5
+    # complex64: the output is written through its float view (interleaved real and imaginary rows)
+    ca, cb = random_array(rng, (200, k), np.complex64), random_array(rng, (k, 300), np.complex64)
+    on, off = _einsum_both_store_paths(tb, monkeypatch, "ij,jk->ik", [T(ca), T(cb)])
+    assert np.array_equal(on, off)
+    assert oracle.rel_frobenius(on, ca.astype(np.complex128) @ cb.astype(np.complex128)) <= 1e-5
+    # an output whose unit-stride mode belongs to neither group's first mode: falls back, same result
+    on, off = _einsum_both_store_paths(tb, monkeypatch, "ijk,kmn->jinm", [a_view, b_view])
+    assert np.array_equal(on, off)
+    assert oracle.rel_frobenius(on, np.transpose(want, (1, 0, 3, 2))) <= 1e-5
