@@ -617,11 +617,15 @@ def wl_dense(env: Env):
     e2e_step, h2d, d2h, e2e_note = None, 0, 0, None
     if not args.no_e2e:
         l_r = l_hi - l_lo
-        ls = min(l_r, max(8, l_r // 8))
-        while l_r % ls:
-            ls -= 1
-        n_slabs = l_r // ls
-        a_slab_bytes = i * j * k * ls * 4
+        # Slabs of 32 l-values while plenty is left, then halving down to 8: the upload paces the
+        # step (PCIe), so what counts at the end is how little work is left once the last slab lands.
+        sizes, rem = [], l_r
+        while rem > 0:
+            sz = 32 if rem >= 64 else (max(8, (rem // 2) // 8 * 8) if rem > 8 else rem)
+            sizes.append(sz)
+            rem -= sz
+        starts = [l_lo + sum(sizes[:q]) for q in range(len(sizes))]
+        n_slabs = len(sizes)
         a_bytes, b_bytes = i * j * k * l_r * 4, k * l_r * m * n * 4
         ha_ptr, _ = pinned(ctx, a_bytes, np.float32)
         hb_ptr, _ = pinned(ctx, b_bytes, np.float32)   # host layout [k, l_r, m, n] column-major
@@ -633,34 +637,61 @@ def wl_dense(env: Env):
         ctx.d2h_2d(C.c_void_p(hb_ptr), k * l_r * 4, b_t.data_ptr() + l_lo * k * 4, k * l * 4, k * l_r * 4, m * n)
         ctx.synchronize()
         acc = Cfull if W == 1 else P
+        # On one GPU the last slab is multiplied in four ranges of n, and each finished quarter of C
+        # starts its way back to the host while the next one is computed.
+        n_chunks = 4 if (W == 1 and n % 4 == 0) else 1
         slab_calls = []
         for s in range(n_slabs):
-            lo = l_lo + s * ls
-            As_, Bs_ = sub(A, 3, lo, lo + ls), sub(B, 1, lo, lo + ls)
-            tree = tb.ContractionTree.optimize(subs, [As_.dims(), Bs_.dims()])
-            slab_calls.append(tb.PreparedEinsum(tree, [As_, Bs_], acc, 1.0, 0.0 if s == 0 else 1.0))
+            lo, hi = starts[s], starts[s] + sizes[s]
+            As_, Bs_ = sub(A, 3, lo, hi), sub(B, 1, lo, hi)
+            beta = 0.0 if s == 0 else 1.0
+            if s == n_slabs - 1 and n_chunks > 1:
+                calls = []
+                for q in range(n_chunks):
+                    n0, n1 = q * n // n_chunks, (q + 1) * n // n_chunks
+                    Bq, Cq = sub(Bs_, 3, n0, n1), sub(acc, 3, n0, n1)
+                    tree = tb.ContractionTree.optimize(subs, [As_.dims(), Bq.dims()])
+                    calls.append(tb.PreparedEinsum(tree, [As_, Bq], Cq, 1.0, beta))
+                slab_calls.append(calls)
+            else:
+                tree = tb.ContractionTree.optimize(subs, [As_.dims(), Bs_.dims()])
+                slab_calls.append([tb.PreparedEinsum(tree, [As_, Bs_], acc, 1.0, beta)])
         copy_ctx = env.copy_ctx
+        c_bytes = c_keep.numel() * 4
 
         def e2e_step():
             events = []
             for s in range(n_slabs):
-                lo = l_lo + s * ls
-                copy_ctx.h2d(a_t.data_ptr() + lo * i * j * k * 4, C.c_void_p(ha_ptr + s * a_slab_bytes), a_slab_bytes)
-                copy_ctx.h2d_2d(b_t.data_ptr() + lo * k * 4, k * l * 4, C.c_void_p(hb_ptr + s * ls * k * 4), k * l_r * 4,
-                                k * ls * 4, m * n)
+                # (one upload stream: with the A and B slabs on two streams the step took 267 ms instead of
+                # 202 ms - under the contraction kernel the uploads reach 42 GB/s of the link's 55.6 either way)
+                lo, off = starts[s], starts[s] - l_lo
+                copy_ctx.h2d(a_t.data_ptr() + lo * i * j * k * 4, C.c_void_p(ha_ptr + off * i * j * k * 4),
+                             i * j * k * sizes[s] * 4)
+                copy_ctx.h2d_2d(b_t.data_ptr() + lo * k * 4, k * l * 4, C.c_void_p(hb_ptr + off * k * 4), k * l_r * 4,
+                                k * sizes[s] * 4, m * n)
                 events.append(copy_ctx.record_event())
             for s in range(n_slabs):
                 ctx.wait_event(events[s])
-                slab_calls[s].run()
-            if W > 1:
-                scatter()
-            ctx.d2h(C.c_void_p(hc_ptr), c_keep.data_ptr(), c_keep.numel() * 4)
+                last = s == n_slabs - 1 and n_chunks > 1
+                for q, call in enumerate(slab_calls[s]):
+                    call.run()
+                    if last:
+                        # this quarter of C is final: it leaves on the copy stream (the uploads are over)
+                        copy_ctx.wait_event(ctx.record_event())
+                        copy_ctx.d2h(C.c_void_p(hc_ptr + q * c_bytes // n_chunks), c_keep.data_ptr() + q * c_bytes // n_chunks,
+                                     c_bytes // n_chunks)
+            if n_chunks == 1:
+                if W > 1:
+                    scatter()
+                ctx.d2h(C.c_void_p(hc_ptr), c_keep.data_ptr(), c_bytes)
             ctx.synchronize()
+            copy_ctx.synchronize()
 
-        h2d, d2h = (a_bytes + b_bytes) * W, c_keep.numel() * 4 * W
-        e2e_note = (f"each rank uploads its 1/{W} of A and B along l in {n_slabs} slabs of {ls} l-values "
+        h2d, d2h = (a_bytes + b_bytes) * W, c_bytes * W
+        e2e_note = (f"each rank uploads its 1/{W} of A and B along l in {n_slabs} slabs of {sizes} l-values "
                     f"(pitched copy for B) on a second stream, multiplies slab s while slab s+1 travels, "
-                    + ("reduce-scatters the partial C and reads its part back" if W > 1 else "and reads C back"))
+                    + ("reduce-scatters the partial C and reads its part back" if W > 1 else
+                       "and reads C back in four parts, each as soon as the last slab has been added to it"))
     # The probe runs once before the workload (cool GPU) and once after (under the power cap the
     # clock has dropped by then); the larger figure is the burst rate.
     tf32_cold = ctx.probe_tf32_tflops()

@@ -43,6 +43,7 @@ struct ContractArgs {
     int debug;
     unsigned* sk_flags;  // per-CTA flags of the in-kernel stream-K reduction (TMA-fed DMMA kernel)
     unsigned sk_epoch;   // a flag is raised when it equals this launch's epoch
+    int sk_two_phase;    // 1: every range parks its sums in its slot; a finishing kernel adds the pieces of a tile
     char* partial;  // 2 slots of one block tile per CTA, used only by ranges that cut a tile
 };
 

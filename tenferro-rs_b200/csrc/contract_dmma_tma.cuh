@@ -254,7 +254,7 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // holds the tile's first k-iteration owns the tile: it collects the contributions of
         // the CTAs after it, in CTA order, and writes C.  Contributions are the first thing a
         // CTA does and collecting is the last, so owners rarely wait; the wait is bounded.
-        if (kb > 0) {
+        if (kb > 0 || g.sk_two_phase) {
             char* P = g.partial + (size_t)blockIdx.x * (BM * BN) * ES;
 #pragma unroll
             for (int i = 0; i < TM; ++i)
@@ -268,10 +268,12 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         else
                             *reinterpret_cast<double*>(q) = acc[i][j][e];
                     }
-            __threadfence();
-            __syncthreads();
-            if (tid == 0)
-                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.sk_flags + blockIdx.x), "r"(g.sk_epoch) : "memory");
+            if (!g.sk_two_phase) {
+                __threadfence();
+                __syncthreads();
+                if (tid == 0)
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(g.sk_flags + blockIdx.x), "r"(g.sk_epoch) : "memory");
+            }
         } else {
             if (ke < g.k_iters) {
                 const int64_t g_last = ((tile + 1) * g.k_iters - 1) / g.iters_per_cta;
@@ -347,6 +349,60 @@ contract_dmma_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
         }
         it += ke - kb;
+    }
+}
+
+// Second phase of the two-launch split over K (outputs of a few tiles with a long K, such as
+// 'abc,bcd->ad' with 64 x 64 outputs and K = 4096): every CTA of the main kernel has parked the
+// sums of its k range in its slot; here one block per (tile, fragment) adds the `pieces` slots of
+// a tile - one value per piece and thread, all loads independent, always in piece order, so the
+// result does not depend on timing - and applies multiplier, alpha and beta.  The thread-to-element
+// map is the main kernel's.  No CTA ever waits for another one.
+template <typename Cfg>
+__global__ void __launch_bounds__(Cfg::NT) dmma_tma_splitk_finish_kernel(ContractArgs g, int pieces) {
+    constexpr bool CPLX = Cfg::kCplx;
+    constexpr int BM = Cfg::BM, BN = Cfg::BN, TN = Cfg::TN, ES = Cfg::ES;
+    const int64_t tile = blockIdx.x;
+    const int f = blockIdx.y, i = f / (2 * TN), j = (f >> 1) % TN, e = f & 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t tm = tile % g.tiles_m, rest = tile / g.tiles_m, tn = rest % g.tiles_n, bb = rest / g.tiles_n;
+    const int64_t m = tm * BM + (warp % Cfg::WARPS_M) * Cfg::WM + 8 * i + (lane >> 2);
+    const int64_t n = tn * BN + (warp / Cfg::WARPS_M) * Cfg::WN + 8 * j + 2 * (lane & 3) + e;
+    const char* P = g.partial + ((size_t)tile * pieces * (BM * BN) + (size_t)f * Cfg::NT + tid) * ES;
+    double xr = 0.0, xi = 0.0;
+#pragma unroll 8
+    for (int s = 0; s < pieces; ++s) {
+        const char* q = P + (size_t)s * (BM * BN) * ES;
+        if (CPLX) {
+            const double2 v = __ldcg(reinterpret_cast<const double2*>(q));
+            xr += v.x;
+            xi += v.y;
+        } else {
+            xr += __ldcg(reinterpret_cast<const double*>(q));
+        }
+    }
+    if (m >= g.M || n >= g.N) return;
+    if (g.mul) {
+        const int64_t off = g.d_b[bb] + g.d_m[m] + g.d_n[n];
+        if (CPLX) apply_mul_c128(g, off, xr, xi);
+        else apply_mul_f64(g, off, xr);
+    }
+    char* p = g.c + (g.c_b[bb] + g.c_m[m] + g.c_n[n]) * (int64_t)ES;
+    const bool read_c = g.beta_re != 0.0 || g.beta_im != 0.0;
+    if (CPLX) {
+        double2 o;
+        o.x = g.alpha_re * xr - g.alpha_im * xi;
+        o.y = g.alpha_re * xi + g.alpha_im * xr;
+        if (read_c) {
+            const double2 old = *reinterpret_cast<const double2*>(p);
+            o.x += g.beta_re * old.x - g.beta_im * old.y;
+            o.y += g.beta_re * old.y + g.beta_im * old.x;
+        }
+        *reinterpret_cast<double2*>(p) = o;
+    } else {
+        double o = g.alpha_re * xr;
+        if (read_c) o += g.beta_re * *reinterpret_cast<const double*>(p);
+        *reinterpret_cast<double*>(p) = o;
     }
 }
 
@@ -438,7 +494,27 @@ static tfb_status run_tma_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractAr
     if (a.total_iters >= ((int64_t)1 << 31)) return TFB_OK;  // the producer indexes k-iterations with 32 bits
     const int64_t slots = ctx->sm_count;  // one CTA per SM
     int64_t grid;
-    if (a.n_tiles % slots == 0 || a.n_tiles >= 16 * slots) {
+    // A handful of tiles with a long K: cut every tile into the same number of k pieces, one CTA
+    // each, and add the pieces in a second, tiny launch.  (In the single-launch form below the
+    // owner of a tile reads all its pieces itself - eight dependent round trips to L2 for 32
+    // pieces - and 'abc,bcd->ad' at 64^4 took 16.4 us; here every load of the sum is independent.)
+    int pieces = 0;
+    if (a.n_tiles * 4 <= slots && a.k_iters >= 16 && env_int("TFB_SK_TWO_PHASE", 1)) {
+        const int64_t want = std::min<int64_t>(std::min<int64_t>(32, slots / a.n_tiles), a.k_iters / 4);
+        a.iters_per_cta = (a.k_iters + want - 1) / want;
+        pieces = (int)((a.k_iters + a.iters_per_cta - 1) / a.iters_per_cta);
+    }
+    if (pieces > 1) {
+        // ranges are per tile: CTA c takes piece c % pieces of tile c / pieces
+        if (a.iters_per_cta * pieces != a.k_iters) {
+            // the kernel cuts the linear (tile, k) space into equal ranges: pieces must divide K's iterations
+            pieces = 0;
+        }
+    }
+    if (pieces > 1) {
+        grid = a.n_tiles * pieces;
+        a.sk_two_phase = 1;
+    } else if (a.n_tiles % slots == 0 || a.n_tiles >= 16 * slots) {
         grid = std::min(a.n_tiles, slots);
         a.iters_per_cta = ((a.n_tiles + grid - 1) / grid) * a.k_iters;
     } else {
@@ -448,7 +524,7 @@ static tfb_status run_tma_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractAr
         // owner one pass over a slot: keep a tile in at most 32 pieces.
         a.iters_per_cta = std::max<int64_t>(a.iters_per_cta, (a.k_iters + 31) / 32);
     }
-    grid = (a.total_iters + a.iters_per_cta - 1) / a.iters_per_cta;
+    if (!a.sk_two_phase) grid = (a.total_iters + a.iters_per_cta - 1) / a.iters_per_cta;
     const bool cuts = a.iters_per_cta % a.k_iters != 0;
     if (cuts) {
         // Scratch slots and flags live with the context (one slot per CTA, reused by every
@@ -480,13 +556,18 @@ static tfb_status run_tma_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractAr
         void* args[] = {(void*)&map_a, (void*)&map_b, (void*)&a, (void*)&status};
         // Owners wait for contributors, so every CTA of the grid has to be resident: a
         // cooperative launch makes the runtime check that (grid <= one CTA per SM).
-        if (cuts && env_int("TFB_SK_COOP", 1))
+        if (cuts && !a.sk_two_phase && env_int("TFB_SK_COOP", 1))
             TFB_CUDA(cudaLaunchCooperativeKernel((const void*)contract_dmma_tma_kernel<Cfg>, dim3((unsigned)grid),
                                                  dim3(Cfg::NT), args, Cfg::SMEM_BYTES, ctx->stream));
         else
             contract_dmma_tma_kernel<Cfg><<<(unsigned)grid, Cfg::NT, Cfg::SMEM_BYTES, ctx->stream>>>(map_a, map_b, a, status);
     }
     TFB_CUDA(cudaGetLastError());
+    if (a.sk_two_phase) {
+        LaunchScope ls(ctx, "contract_dmma_finish");
+        dmma_tma_splitk_finish_kernel<Cfg><<<dim3((unsigned)a.n_tiles, Cfg::TM * Cfg::TN * 2), Cfg::NT, 0, ctx->stream>>>(a, pieces);
+        TFB_CUDA(cudaGetLastError());
+    }
     *declined = false;
     return TFB_OK;
 }
