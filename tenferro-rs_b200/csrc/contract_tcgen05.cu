@@ -93,17 +93,19 @@ struct TileRows {
     int valid, f1, f2;
 };
 __device__ __forceinline__ TileRows tile_rows(const TcGeom& g, int64_t t, int rows_per_tile, int64_t total) {
+    // 32-bit divisions: tile numbers and row counts stay below 2^31 (checked on the host)
     TileRows r;
+    const uint32_t t32 = (uint32_t)t;
     if (g.pack) {
-        r.base = t * rows_per_tile;
+        r.base = (int64_t)t32 * rows_per_tile;
         r.f1 = 0;
-        r.f2 = (int)(r.base / g.e1);
+        r.f2 = (int)((uint32_t)r.base / (uint32_t)g.e1);
         r.valid = (int)min((int64_t)rows_per_tile, total - r.base);
     } else {
-        const int64_t f2 = t / g.tiles1;
-        r.f1 = (int)(t - f2 * g.tiles1) * rows_per_tile;
+        const uint32_t f2 = t32 / (uint32_t)g.tiles1;
+        r.f1 = (int)(t32 - f2 * (uint32_t)g.tiles1) * rows_per_tile;
         r.f2 = (int)f2;
-        r.base = f2 * g.e1 + r.f1;
+        r.base = (int64_t)f2 * g.e1 + r.f1;
         r.valid = min(rows_per_tile, g.e1 - r.f1);
     }
     return r;
@@ -541,12 +543,33 @@ struct PairWork {
     TileRows tr_m;      // this CTA's rows
     TileRows tr_n[2];   // the two column halves of the tile
 };
+// decode_tile in 32-bit arithmetic (the host keeps the number of work items below 2^31): a 64-bit
+// division costs several times a 32-bit one, and these run in the threads whose latency the
+// pipeline feels.
+__device__ __forceinline__ TileCoord decode_tile32(uint32_t tile, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m) {
+    TileCoord t;
+    const uint32_t tiles_per_batch = tiles_m * tiles_n;
+    const uint32_t batch = tile / tiles_per_batch;
+    tile -= batch * tiles_per_batch;
+    const uint32_t group_sz = group_m * tiles_n;
+    const uint32_t grp = tile / group_sz;
+    const uint32_t first_m = grp * group_m;
+    const uint32_t rows_in_group = min(group_m, tiles_m - first_m);
+    const uint32_t in_grp = tile - grp * group_sz;
+    const uint32_t tn = in_grp / rows_in_group;
+    t.batch = batch;
+    t.tm = first_m + (in_grp - tn * rows_in_group);
+    t.tn = tn;
+    return t;
+}
 __device__ __forceinline__ PairWork pair_work(const TcArgs& g, int64_t w, uint32_t rank) {
     PairWork pw;
     const int64_t tiles_mp = (g.tiles_m + 1) / 2, tiles_np = (g.tiles_n + 1) / 2;
-    pw.split = (int)(w % g.k_split);
-    pw.pair_tile = w / g.k_split;
-    const TileCoord tc = decode_tile(pw.pair_tile, tiles_mp, tiles_np, g.group_m);
+    const uint32_t w32 = (uint32_t)w, ks = (uint32_t)g.k_split;
+    const uint32_t pt = w32 / ks;
+    pw.split = (int)(w32 - pt * ks);
+    pw.pair_tile = pt;
+    const TileCoord tc = decode_tile32(pt, (uint32_t)tiles_mp, (uint32_t)tiles_np, (uint32_t)g.group_m);
     pw.batch = tc.batch;
     // A tile past the end (odd tile counts) has coordinates outside the tensor: TMA fills it
     // with zeros and nothing of it is stored.
@@ -641,45 +664,63 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // ---------------------------------------------------------------- TMA producer (each CTA its own tiles)
         if (lane == 0) {
             uint32_t it = 0;
+            PairWork pw_next = pair_work(g, w0, rank);
             for (int64_t w = w0; w < n_work; w += wstep) {
-            const PairWork pw = pair_work(g, w, rank);
+            const PairWork pw = pw_next;
             const TileRows tr_m = pw.tr_m, tr_nl = rank ? pw.tr_n[1] : pw.tr_n[0];  // tr_nl: the half of B this CTA stages
             const int64_t bb = pw.batch;
+            // Coordinates of the four 32-row boxes of an MN-major tile, once per work item: with packed
+            // tiling every box finds its own (inner, outer) pair from its linear row, and a division
+            // per box and k-block in this thread delays every load of the tile (an i-slice with 64 rows
+            // per run: 86 ms instead of 72 ms for M = 8192, N = 16384, K = 65536).
+            int a_f1[kBM / 32], a_f2[kBM / 32], b_f1[4], b_f2[4];
+#pragma unroll
+            for (int c = 0; c < kBM / 32; ++c) {
+                a_f1[c] = tr_m.f1 + 32 * c;
+                a_f2[c] = tr_m.f2;
+                if (g.a.pack) {
+                    const int64_t row = tr_m.base + 32 * c;
+                    a_f2[c] = (int)(row / g.a.e1);
+                    a_f1[c] = (int)(row - (int64_t)a_f2[c] * g.a.e1);
+                }
+                b_f1[c] = tr_nl.f1 + 32 * c;
+                b_f2[c] = tr_nl.f2;
+                if (g.b.pack) {
+                    const int64_t row = tr_nl.base + 32 * c;
+                    b_f2[c] = (int)(row / g.b.e1);
+                    b_f1[c] = (int)(row - (int64_t)b_f2[c] * g.b.e1);
+                }
+            }
+            // k coordinates advance without a division per k-block (this thread's latency is the loads')
+            int k2 = pw.kb_first / g.k_blocks1, k1b = pw.kb_first - k2 * g.k_blocks1;
             for (int kb = 0; kb < pw.num_kb; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t use = it / STAGES;
+                const int k1 = k1b * kBK;
                 mbar_wait(bar_empty(s), (use & 1) ^ 1, g.status, 0x111);
                 const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
                 const uint32_t b_dst = a_dst + Cfg::A_BYTES;
                 mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
-                const int kg = pw.kb_first + kb;
-                const int k2 = kg / g.k_blocks1, k1 = (kg - k2 * g.k_blocks1) * kBK;
                 if (g.a.mn_major) {
-                    for (int c = 0; c < kBM / 32; ++c) {
-                        int f1 = tr_m.f1 + 32 * c, f2 = tr_m.f2;
-                        if (g.a.pack) {
-                            const int64_t row = tr_m.base + 32 * c;
-                            f2 = (int)(row / g.a.e1);
-                            f1 = (int)(row - (int64_t)f2 * g.a.e1);
-                        }
-                        tma_load_5d(a_dst + c * 4096, &map_a, bar_full(s), f1, f2, k1, k2, (int)bb);
-                    }
+#pragma unroll
+                    for (int c = 0; c < kBM / 32; ++c)
+                        tma_load_5d(a_dst + c * 4096, &map_a, bar_full(s), a_f1[c], a_f2[c], k1, k2, (int)bb);
                 } else {
                     tma_load_5d(a_dst, &map_a, bar_full(s), k1, k2, tr_m.f1, tr_m.f2, (int)bb);
                 }
                 if (g.b.mn_major) {
-                    for (int c = 0; c < 128 / 32; ++c) {
-                        int f1 = tr_nl.f1 + 32 * c, f2 = tr_nl.f2;
-                        if (g.b.pack) {
-                            const int64_t row = tr_nl.base + 32 * c;
-                            f2 = (int)(row / g.b.e1);
-                            f1 = (int)(row - (int64_t)f2 * g.b.e1);
-                        }
-                        tma_load_5d(b_dst + c * 4096, &map_b, bar_full(s), f1, f2, k1, k2, (int)bb);
-                    }
+#pragma unroll
+                    for (int c = 0; c < 128 / 32; ++c)
+                        tma_load_5d(b_dst + c * 4096, &map_b, bar_full(s), b_f1[c], b_f2[c], k1, k2, (int)bb);
                 } else {
                     tma_load_5d(b_dst, &map_b, bar_full(s), k1, k2, tr_nl.f1, tr_nl.f2, (int)bb);
                 }
+                if (++k1b == g.k_blocks1) {
+                    k1b = 0;
+                    ++k2;
+                }
+                // the next work item is decoded behind this one's first loads, not in front of its own
+                if (kb == 0 && w + wstep < n_work) pw_next = pair_work(g, w + wstep, rank);
             }
             }
         }
@@ -1597,19 +1638,8 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
             if (o.geom.pack) return false;
             return (total / o.geom.e1) * o.geom.tiles1 * rows > total + total / 2;
         };
-        // A unit-stride free mode of at most 256 bytes with a gap behind it (what slicing the
-        // fastest index of an operand leaves: rows of 64 floats at a pitch of 128) is read through
-        // only part of the address space's interleaving - every access has the same low address
-        // bits - and the tiles arrive late: measured 84.8 ms against 72.3 ms for the same slice
-        // stored densely (M = 8192, N = 16384, K = 65536).  Repacking costs about 1 ms there.
-        auto gappy = [](const std::vector<Mode>& free, int tns) {
-            return free.size() == 2 && free[0].s[tns] == 1 && free[0].extent <= 64 &&
-                   free[1].s[tns] != free[0].extent;
-        };
-        const int force_pack = env_int("TFB_TC_REPACK", 0);  // bit 0: A, bit 1: B; 4: never for gaps
-        const bool gaps = !(force_pack & 4);
-        const bool pack_a = wasteful(a, M, kBM) || (gaps && gappy(p.m, 0)) || (force_pack & 1);
-        const bool pack_b = wasteful(b, N, rows_b) || (gaps && gappy(p.n, 1)) || (force_pack & 2);
+        const int force_pack = env_int("TFB_TC_REPACK", 0);  // bit 0: A, bit 1: B (experiments)
+        const bool pack_a = wasteful(a, M, kBM) || (force_pack & 1), pack_b = wasteful(b, N, rows_b) || (force_pack & 2);
         if (pack_a || pack_b) {
             TFB_TRY(get_tables(ctx, p, &t));
             ContractArgs ca;
