@@ -664,6 +664,8 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // ---------------------------------------------------------------- TMA producer (each CTA its own tiles)
         if (lane == 0) {
             uint32_t it = 0;
+            int p_stage = 0;
+            uint32_t p_parity = 0;
             PairWork pw_next = pair_work(g, w0, rank);
             for (int64_t w = w0; w < n_work; w += wstep) {
             const PairWork pw = pw_next;
@@ -694,12 +696,17 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             // k coordinates advance without a division per k-block (this thread's latency is the loads')
             int k2 = pw.kb_first / g.k_blocks1, k1b = pw.kb_first - k2 * g.k_blocks1;
             for (int kb = 0; kb < pw.num_kb; ++kb, ++it) {
-                const int s = it % STAGES;
-                const uint32_t use = it / STAGES;
+                // stage number and pass parity are counted, not divided out: whatever this thread
+                // does between the stage becoming free and the loads going out delays the tile
+                const int s = p_stage;
                 const int k1 = k1b * kBK;
-                mbar_wait(bar_empty(s), (use & 1) ^ 1, g.status, 0x111);
                 const uint32_t a_dst = ring + s * Cfg::STAGE_BYTES;
                 const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+                mbar_wait(bar_empty(s), p_parity ^ 1, g.status, 0x111);
+                if (++p_stage == STAGES) {
+                    p_stage = 0;
+                    p_parity ^= 1;
+                }
                 mbar_expect_tx(bar_full(s), Cfg::A_BYTES + Cfg::B_BYTES);
                 if (g.a.mn_major) {
 #pragma unroll
@@ -735,35 +742,47 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t a_lay = g.a.mn_major ? 1u : 2u, b_lay = g.b.mn_major ? 1u : 2u;
             const uint32_t a_step = g.a.mn_major ? 1024u : 32u, b_step = g.b.mn_major ? 1024u : 32u;
             uint32_t it = 0, ch0 = 0;  // k-blocks and chunks issued before this work item
+            // Descriptors of stage 0, k-step 0; those of stage s and k-step ks differ only in the start
+            // address field (bits 0-13, in 16-byte units), so they follow by one addition each.  What
+            // this thread computes between a stage being converted and its first MMA delays the tile.
+            const uint64_t da_big0 = smem_desc(ring, a_lbo, a_sbo, a_lay);
+            const uint64_t db_big0 = smem_desc(ring + Cfg::A_BYTES, b_lbo, b_sbo, b_lay);
+            const uint64_t da_small0 = smem_desc(ring + Cfg::A_BYTES + Cfg::B_BYTES, a_lbo, a_sbo, a_lay);
+            const uint64_t db_small0 = smem_desc(ring + 2 * Cfg::A_BYTES + Cfg::B_BYTES, b_lbo, b_sbo, b_lay);
+            const uint32_t a_inc = a_step >> 4, b_inc = b_step >> 4;
+            int m_stage = 0;
+            uint32_t m_parity = 0;
             for (int64_t w = w0; w < n_work; w += wstep) {
             const int num_kb = pair_num_kb(g, w);
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                const int s = it % STAGES;
-                const uint32_t use = it / STAGES;
+                const int s = m_stage;
                 const uint32_t chunk = ch0 + kb / kChunk;
                 const int buf = chunk & 1;
                 const bool chunk_first = kb % kChunk == 0;
                 const bool chunk_last = (kb % kChunk == kChunk - 1) || kb == num_kb - 1;
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t stage_off = (uint32_t)(s * (Cfg::STAGE_BYTES >> 4));
+                uint64_t da_big = da_big0 + stage_off, da_small = da_small0 + stage_off;
+                uint64_t db_big = db_big0 + stage_off, db_small = db_small0 + stage_off;
                 if (chunk_first && chunk >= 2) {
                     mbar_wait_cluster(bar_promoted(buf), ((uint32_t)(chunk >> 1) - 1) & 1, g.status, 0x115);
                     tc_fence_after();
                 }
-                mbar_wait_cluster(bar_split(s), use & 1, g.status, 0x112);
+                mbar_wait_cluster(bar_split(s), m_parity, g.status, 0x112);
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                const uint32_t a_big = ring + s * Cfg::STAGE_BYTES;
-                const uint32_t b_big = a_big + Cfg::A_BYTES;
-                const uint32_t a_small = b_big + Cfg::B_BYTES;
-                const uint32_t b_small = a_small + Cfg::A_BYTES;
+                if (++m_stage == STAGES) {
+                    m_stage = 0;
+                    m_parity ^= 1;
+                }
 #pragma unroll
                 for (int ks = 0; ks < kBK / 8; ++ks) {
-                    const uint64_t da_big = smem_desc(a_big + ks * a_step, a_lbo, a_sbo, a_lay);
-                    const uint64_t da_small = smem_desc(a_small + ks * a_step, a_lbo, a_sbo, a_lay);
-                    const uint64_t db_big = smem_desc(b_big + ks * b_step, b_lbo, b_sbo, b_lay);
-                    const uint64_t db_small = smem_desc(b_small + ks * b_step, b_lbo, b_sbo, b_lay);
                     tc_mma_tf32_pair(tmem_d, da_small, db_big, idesc, !(chunk_first && ks == 0));
                     tc_mma_tf32_pair(tmem_d, da_big, db_small, idesc, 1);
                     tc_mma_tf32_pair(tmem_d, da_big, db_big, idesc, 1);
+                    da_big += a_inc;
+                    da_small += a_inc;
+                    db_big += b_inc;
+                    db_small += b_inc;
                 }
                 tc_commit_pair(bar_empty(s));
                 tc_commit_pair(map_to_cta(bar_empty(s), 1));
@@ -1030,7 +1049,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
             char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
             constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
-#pragma unroll 4
+#pragma unroll 8
             for (int c = t; c < CHUNKS; c += kSplitThreads) {
                 const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
                 float4 sm;
