@@ -779,7 +779,7 @@ def wl_grouped(env: Env):
         "step": step, "work": flops_all, "read_result": read_result, "e2e_step": e2e_step,
         "h2d": float(4 * (table[:, 0] * table[:, 1] + table[:, 1] * table[:, 2]).sum()),
         "d2h": float(4 * (table[:, 0] * table[:, 2]).sum()),
-        "kernel": "grouped_tf32x3", "kernels_any": ["grouped_fma", "grouped_tf32x3", "grouped_simt"],
+        "kernel": "grouped_tf32x3", "kernels_any": ["grouped_tf32x3", "grouped_tcgen05", "grouped_simt"],
         "kernel_label": "grouped_f32_kernel (persistent CTAs, host-built stage table, double-buffered cp.async panels)",
         "per_launch": float(bytes_p[lo:hi].sum()), "bound": "hbm",
         "peak": (lambda: hbm) if hbm else ctx.probe_hbm_gbs,

@@ -199,12 +199,17 @@ struct PoolBlock {
     tfb_status alloc(tfb_ctx* c, size_t bytes);
 };
 
-// Device-resident schedule of one problem table for the tensor-core grouped kernel.
+// Device-resident schedule of one problem table for the tensor-core grouped kernels.
 struct GroupedFast {
     PoolBlock mem;
     int64_t total_units = 0;
     int grid = 0;
+    int pitch = 0;         // tcgen05: records per CTA
+    bool tcgen05 = false;  // which kernel the schedule is for
 };
+tfb_status grouped_tcgen05_prepare(tfb_ctx* ctx, size_t n, const tfb_gemm_problem* problems, GroupedFast* out,
+                                   bool* declined);
+tfb_status grouped_tcgen05_run(tfb_ctx* ctx, const GroupedFast& f, Scalar alpha, Scalar beta, bool* declined);
 tfb_status grouped_tf32_prepare(tfb_ctx* ctx, size_t n, const tfb_gemm_problem* problems, GroupedFast* out,
                                 bool* declined);
 tfb_status grouped_tf32_run(tfb_ctx* ctx, const GroupedFast& f, Scalar alpha, Scalar beta, bool* declined);

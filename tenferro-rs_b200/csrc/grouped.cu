@@ -169,8 +169,14 @@ tfb_status prepare(tfb_ctx* ctx, int dtype, size_t n, const tfb_gemm_problem* pr
     plan->dtype = dtype;
     plan->problems.assign(problems, problems + n);
     if (dtype == TFB_F32) {
+        // The mma.sync kernel is the faster one on the tables it takes (dims in multiples of 16, K up to
+        // 128); the tcgen05 kernel takes any dims with 16-byte aligned columns and K up to 512; the
+        // SIMT kernel takes everything.
+        const bool tcgen05_first = env_int("TFB_GROUPED_PREFER_TCGEN05", 0) != 0;
         bool declined = true;
-        TFB_TRY(grouped_tf32_prepare(ctx, n, problems, &plan->schedule, &declined));
+        if (tcgen05_first) TFB_TRY(grouped_tcgen05_prepare(ctx, n, problems, &plan->schedule, &declined));
+        if (declined) TFB_TRY(grouped_tf32_prepare(ctx, n, problems, &plan->schedule, &declined));
+        if (declined && !tcgen05_first) TFB_TRY(grouped_tcgen05_prepare(ctx, n, problems, &plan->schedule, &declined));
         plan->fast = !declined;
     }
     return TFB_OK;
@@ -181,7 +187,10 @@ tfb_status run(tfb_grouped_plan* plan, tfb::Scalar alpha, tfb::Scalar beta) {
     DeviceGuard g(plan->ctx->device);
     if (plan->fast) {
         bool declined = true;
-        TFB_TRY(grouped_tf32_run(plan->ctx, plan->schedule, alpha, beta, &declined));
+        if (plan->schedule.tcgen05)
+            TFB_TRY(grouped_tcgen05_run(plan->ctx, plan->schedule, alpha, beta, &declined));
+        else
+            TFB_TRY(grouped_tf32_run(plan->ctx, plan->schedule, alpha, beta, &declined));
         if (!declined) return TFB_OK;
     }
     return grouped_simt(plan->ctx, plan->dtype, plan->problems.size(), plan->problems.data(), alpha, beta);

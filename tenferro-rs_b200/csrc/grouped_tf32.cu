@@ -1,4 +1,4 @@
-// Grouped f32 products on the tensor cores: the fast path of tfb_grouped_gemm for ragged
+// Grouped f32 products on the tensor cores (mma.sync): the fast path of tfb_grouped_gemm for ragged
 // batches of small column-major problems (every dimension a multiple of 16, at most 128
 // deep - e.g. 4096 problems with dims drawn from {16, 32, 64, 128}).
 //
@@ -20,8 +20,10 @@
 //   * the tile leaves from registers in whole 32-byte sectors.
 // Three CTAs per SM; nothing ever waits on another CTA.
 //
-// tcgen05 is the wrong tool here: its 64/128-row tiles would be mostly padding for 16 - 64 row
-// problems, and there is no reuse for TMEM to hold.
+// The tcgen05 form of this kernel (grouped_tcgen05.cu) is slower on these tables - 96 us against
+// 54 for 4096 problems - because 3xTF32 from shared memory is bound by shared-memory bandwidth
+// and by the cost of issuing one MMA per 8 of K, and its 128-row tiles are mostly padding for
+// 16 - 64 row problems; it takes the tables this kernel declines.
 //
 // Semantics: C_p = alpha * A_p B_p + beta * C_p per problem, the formula of
 // PrimDescriptor::BatchedGemm (tenferro-prims/src/lib.rs:156-168).
