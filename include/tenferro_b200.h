@@ -230,6 +230,12 @@ tfb_status tfb_probe_tf32_tflops(tfb_ctx* ctx, double* tflops);
 /* The same loop launched back to back for `seconds` (at most 30); reports the rate of the last
  * quarter of the run: what the tensor pipe sustains under the board's power limit. */
 tfb_status tfb_probe_tf32_tflops_sustained(tfb_ctx* ctx, double seconds, double* tflops);
+/* What one small tcgen05.mma costs: `issuers` threads (1..4, one per warp) of every CTA issue
+ * 480 TF32 MMAs of shape m x n x 8 between them (m 64 or 128, n a multiple of 16 up to 256; 128
+ * with several issuers), each thread into its own accumulator.  issue_cycles = SM clocks per MMA
+ * for the issuing thread, complete_cycles = SM clocks per MMA until all had completed.  The
+ * figure behind the grouped kernels' choice of tile and issuer count. */
+tfb_status tfb_probe_mma_issue_cycles(tfb_ctx* ctx, int m, int n, int issuers, double* issue_cycles, double* complete_cycles);
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): launches one CTA
  * that waits, for at most `polls` polls (1..2^20), on an mbarrier nothing arrives on.  The wait
  * runs out, the kernel records status code 0x7e57 and returns; the next tfb_ctx_synchronize

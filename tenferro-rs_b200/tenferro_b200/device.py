@@ -252,6 +252,12 @@ class Context:
         """Launch the kernel whose bounded wait must run out; the next synchronize() raises DeviceError."""
         check(lib.tfb_selftest_wait_expiry(self.handle, polls))
 
+    def probe_mma_issue_cycles(self, m: int, n: int, issuers: int = 1):
+        """(clocks per tcgen05.mma m x n x 8 for the issuing thread, clocks per MMA until all completed)."""
+        a, b = C.c_double(), C.c_double()
+        check(lib.tfb_probe_mma_issue_cycles(self.handle, m, n, issuers, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     def probe_hbm_gbs(self) -> float:
         v = C.c_double()
         check(lib.tfb_probe_hbm_gbs(self.handle, C.byref(v)))

@@ -225,3 +225,19 @@ def test_complex128_imaginary_part_alone(tb, oracle):
     assert errs["three"][0] <= 1e-12 and errs["four"][0] <= 1e-12   # the contract's tolerance, both
     assert errs["four"][1] <= 1e-12                                  # four products: Im to its own size
     assert errs["three"][1] <= 1e-6                                  # three products: Im keeps ~half its digits
+
+
+def test_mma_issue_probe_reports_plausible_clocks(tb):
+    """tfb_probe_mma_issue_cycles: a small tcgen05.mma costs its issuing thread tens of clocks, more
+    issuers shorten the time per MMA of the CTA, and shapes the probe does not take are refused."""
+    ctx = tb.Context.get(0)
+    issue1, done1 = ctx.probe_mma_issue_cycles(128, 16, 1)
+    issue2, done2 = ctx.probe_mma_issue_cycles(128, 16, 2)
+    assert 20.0 <= issue1 <= 400.0 and 20.0 <= done1 <= 400.0, (issue1, done1)
+    assert done2 < done1, (done1, done2)
+    big, _ = ctx.probe_mma_issue_cycles(128, 256, 1)
+    assert big >= 100.0, big  # 128 x 256 x 8 is 128 clocks of tensor-pipe work
+    for bad in ((96, 16, 1), (128, 24, 1), (128, 256, 2), (128, 16, 5)):
+        with pytest.raises(tb.InvalidArgument):
+            ctx.probe_mma_issue_cycles(*bad)
+    ctx.synchronize()
