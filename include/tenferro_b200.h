@@ -243,6 +243,21 @@ tfb_status tfb_probe_mma_issue_cycles(tfb_ctx* ctx, int m, int n, int issuers, d
  * in the message and clears it, and the context keeps working. */
 tfb_status tfb_selftest_wait_expiry(tfb_ctx* ctx, unsigned polls);
 
+/* Capture and replay of a sequence of calls (no counterpart in the reference, whose executor
+ * enqueues node by node; for launch-bound loops such as one site of an MPS sweep).  Between
+ * capture_begin and capture_end the calls made on `ctx` enqueue nothing: their
+ * launches, pool allocations and copies become the nodes of a graph, which capture_end
+ * instantiates.  tfb_graph_launch replays it on the context's stream, with the pointers and
+ * scalars the captured calls were given.  The sequence must have run once before it is
+ * captured (plans, offset tables and kernel attributes are set up on first use with calls that
+ * capture does not allow); synchronize, profile_begin and set_stream are refused while capturing, and
+ * events recorded then mark nothing (they read as complete). */
+typedef struct tfb_graph tfb_graph;
+tfb_status tfb_ctx_capture_begin(tfb_ctx* ctx);
+tfb_status tfb_ctx_capture_end(tfb_ctx* ctx, tfb_graph** out);
+tfb_status tfb_graph_launch(tfb_graph* graph);
+void tfb_graph_destroy(tfb_graph* graph);
+
 /* CompletionEvent (tenferro-tensor/src/lib.rs:301-309, 677-713). */
 tfb_status tfb_event_record(tfb_ctx* ctx, tfb_event** out);    /* marks all work enqueued so far */
 tfb_status tfb_event_wait(tfb_ctx* ctx, tfb_event* ev);        /* later work of ctx waits for ev; host does not block */

@@ -63,6 +63,21 @@ impl Context {
         check(unsafe { sys::tfb_ctx_synchronize(self.raw) })
     }
 
+    /// Records what `f` enqueues on this context into a graph instead of running it
+    /// (`tfb_ctx_capture_begin` / `_end`).  The sequence must have run once before: first uses
+    /// build plans and offset tables with calls that capture does not allow.
+    pub fn capture<F: FnOnce() -> Result<()>>(&self, f: F) -> Result<CapturedGraph> {
+        // SAFETY: `raw` is a live context for the lifetime of `self`.
+        check(unsafe { sys::tfb_ctx_capture_begin(self.raw) })?;
+        let body = f();
+        let mut graph = core::ptr::null_mut();
+        // SAFETY: valid context and out-pointer; ends the capture whatever `f` returned.
+        let ended = check(unsafe { sys::tfb_ctx_capture_end(self.raw, &mut graph) });
+        body?;
+        ended?;
+        Ok(CapturedGraph { raw: graph })
+    }
+
     /// Marks all work enqueued so far.
     pub fn record_event(&self) -> Result<CompletionEvent> {
         let mut ev = core::ptr::null_mut();
@@ -102,6 +117,29 @@ impl Drop for Context {
     fn drop(&mut self) {
         // SAFETY: the handle came from tfb_ctx_create and is dropped once.
         unsafe { sys::tfb_ctx_destroy(self.raw) };
+    }
+}
+
+/// A captured sequence of calls (`tfb_graph_*`); `launch` replays it on the context's stream with
+/// the pointers and scalars the captured calls were given.
+pub struct CapturedGraph {
+    pub(crate) raw: *mut sys::tfb_graph,
+}
+
+// SAFETY: the handle is only read by `launch`; CUDA graph launches may come from any thread.
+unsafe impl Send for CapturedGraph {}
+
+impl CapturedGraph {
+    pub fn launch(&self) -> Result<()> {
+        // SAFETY: live handle.
+        check(unsafe { sys::tfb_graph_launch(self.raw) })
+    }
+}
+
+impl Drop for CapturedGraph {
+    fn drop(&mut self) {
+        // SAFETY: the handle came from tfb_ctx_capture_end and is destroyed once.
+        unsafe { sys::tfb_graph_destroy(self.raw) }
     }
 }
 

@@ -18,5 +18,5 @@ mod error;
 
 pub use backend::{CudaBackend, CudaPlan};
 pub use buffer::CudaBuffer;
-pub use device::{CompletionEvent, Context};
+pub use device::{CapturedGraph, CompletionEvent, Context};
 pub use error::check;

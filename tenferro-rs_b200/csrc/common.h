@@ -85,6 +85,14 @@ struct tfb_ctx {
         cudaEvent_t start, stop;
     };
     std::vector<ProfRec> prof;
+    bool capturing = false;  // between tfb_ctx_capture_begin and _end: launches are recorded, not run
+};
+
+// A captured sequence of this library's launches, instantiated for replay (tfb_graph_*).
+struct tfb_graph {
+    tfb_ctx* ctx = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
 };
 
 struct tfb_event {

@@ -170,6 +170,7 @@ unsigned long long tfb_kernel_launch_count(void) { return launch_count(); }
 
 tfb_status tfb_ctx_profile_begin(tfb_ctx* ctx) {
     if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_profile_begin: ctx is NULL");
+    if (ctx->capturing) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_profile_begin: the context is capturing");
     for (auto& r : ctx->prof) {
         cudaEventDestroy(r.start);
         cudaEventDestroy(r.stop);
@@ -257,6 +258,7 @@ tfb_status tfb_ctx_set_stream(tfb_ctx* ctx, void* stream) {
     if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_set_stream: ctx is NULL");
     cudaStream_t next = stream ? (cudaStream_t)stream : ctx->own_stream;
     if (next == ctx->stream) return TFB_OK;
+    if (ctx->capturing) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_set_stream: the context is capturing");
     // Work enqueued on the new stream comes after everything already enqueued on the old one:
     // pool blocks, the offset tables and the stream-K scratch of this context are all ordered
     // by "the context's stream", so the switch must not let two of its launches overlap.
@@ -271,8 +273,70 @@ tfb_status tfb_ctx_set_stream(tfb_ctx* ctx, void* stream) {
     return TFB_OK;
 }
 
+// ---- capture and replay.  The context's stream goes into CUDA stream capture: every launch,
+// pool allocation and copy this library enqueues until capture_end becomes a node of a graph
+// instead of running.  Plans, offset tables and kernel attributes are host-side state that the
+// first call of a kind sets up with calls capture does not allow, so the sequence has to have
+// run once before it is captured.
+tfb_status tfb_ctx_capture_begin(tfb_ctx* ctx) {
+    if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_capture_begin: ctx is NULL");
+    if (ctx->capturing) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_capture_begin: the context is capturing already");
+    if (ctx->profiling) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_capture_begin: end the launch profile first");
+    DeviceGuard g(ctx->device);
+    // Relaxed mode: the library's host-side bookkeeping between launches (event queries on the offset
+    // tables' upload, attribute calls) is not work on the captured stream and stays allowed.
+    TFB_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+    ctx->capturing = true;
+    return TFB_OK;
+}
+
+tfb_status tfb_ctx_capture_end(tfb_ctx* ctx, tfb_graph** out) {
+    if (!ctx || !out) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_capture_end: NULL argument");
+    *out = nullptr;
+    if (!ctx->capturing) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_capture_end: the context is not capturing");
+    DeviceGuard g(ctx->device);
+    ctx->capturing = false;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (e != cudaSuccess || !graph) {
+        cudaGetLastError();  // a call that capture does not allow has ended it; the stream is usable again
+        return fail(TFB_ERR_DEVICE, "the captured sequence contained a call that cannot be captured (%s): "
+                                    "run the sequence once before capturing it", cudaGetErrorString(e));
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        return fail(TFB_ERR_DEVICE, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+    tfb_graph* gr = new tfb_graph;
+    gr->ctx = ctx;
+    gr->graph = graph;
+    gr->exec = exec;
+    *out = gr;
+    return TFB_OK;
+}
+
+tfb_status tfb_graph_launch(tfb_graph* graph) {
+    if (!graph || !graph->exec) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_graph_launch: graph is NULL");
+    if (graph->ctx->capturing) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_graph_launch: the context is capturing");
+    DeviceGuard g(graph->ctx->device);
+    count_launch(1);
+    TFB_CUDA(cudaGraphLaunch(graph->exec, graph->ctx->stream));
+    return TFB_OK;
+}
+
+void tfb_graph_destroy(tfb_graph* graph) {
+    if (!graph) return;
+    DeviceGuard g(graph->ctx->device);
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    if (graph->graph) cudaGraphDestroy(graph->graph);
+    delete graph;
+}
+
 tfb_status tfb_ctx_synchronize(tfb_ctx* ctx) {
     if (!ctx) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_synchronize: ctx is NULL");
+    if (ctx->capturing) return fail(TFB_ERR_INVALID_ARGUMENT, "tfb_ctx_synchronize: the context is capturing");
     DeviceGuard g(ctx->device);
     TFB_CUDA(cudaStreamSynchronize(ctx->stream));
     // Kernels with bounded waits report through this word instead of trapping.
@@ -401,7 +465,10 @@ tfb_status tfb_event_record(tfb_ctx* ctx, tfb_event** out) {
     std::unique_ptr<tfb_event> ev(new tfb_event);
     ev->device = ctx->device;
     TFB_CUDA(cudaEventCreate(&ev->ev));
-    cudaError_t e = cudaEventRecord(ev->ev, ctx->stream);
+    // While the context is capturing nothing is enqueued, so there is nothing to mark: the event stays
+    // unrecorded, which reads as complete (an event recorded into the capture could be neither
+    // queried nor waited for from outside it).
+    cudaError_t e = ctx->capturing ? cudaSuccess : cudaEventRecord(ev->ev, ctx->stream);
     if (e != cudaSuccess) {
         cudaEventDestroy(ev->ev);
         return fail(TFB_ERR_DEVICE, "cudaEventRecord failed: %s", cudaGetErrorString(e));

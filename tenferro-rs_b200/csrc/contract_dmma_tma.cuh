@@ -548,7 +548,15 @@ static tfb_status run_tma_cfg(tfb_ctx* ctx, const ContractProblem& p, ContractAr
         }
         a.partial = (char*)ctx->sk_partial;
         a.sk_flags = ctx->sk_flags;
-        a.sk_epoch = ++ctx->sk_epoch;
+        if (ctx->capturing) {
+            // A replayed launch would meet the flags its last run raised: a captured launch clears
+            // them first and uses an epoch no live launch has.
+            TFB_CUDA(cudaMemsetAsync(ctx->sk_flags, 0, (size_t)grid * sizeof(unsigned), ctx->stream));
+            a.sk_epoch = 0xffffffffu;
+        } else {
+            a.sk_epoch = ++ctx->sk_epoch;
+            if (a.sk_epoch == 0xffffffffu) a.sk_epoch = ctx->sk_epoch = 1;
+        }
     }
     {
         LaunchScope ls(ctx, "contract_dmma");

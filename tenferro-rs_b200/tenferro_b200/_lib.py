@@ -96,6 +96,10 @@ PROTOTYPES = {
     "tfb_probe_tf32_tflops": (C.c_int, [_VP, C.POINTER(C.c_double)]),
     "tfb_probe_tf32_tflops_sustained": (C.c_int, [_VP, C.c_double, C.POINTER(C.c_double)]),
     "tfb_selftest_wait_expiry": (C.c_int, [_VP, C.c_uint]),
+    "tfb_ctx_capture_begin": (C.c_int, [_VP]),
+    "tfb_ctx_capture_end": (C.c_int, [_VP, C.POINTER(_VP)]),
+    "tfb_graph_launch": (C.c_int, [_VP]),
+    "tfb_graph_destroy": (None, [_VP]),
     "tfb_probe_mma_issue_cycles": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "tfb_event_record": (C.c_int, [_VP, _VPP]),
     "tfb_event_wait": (C.c_int, [_VP, _VP]),

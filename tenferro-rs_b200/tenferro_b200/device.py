@@ -267,6 +267,16 @@ class Context:
     def kernel_launch_count() -> int:
         return int(lib.tfb_kernel_launch_count())
 
+    def capture_begin(self) -> None:
+        """Calls on this context (from this thread) are recorded into a graph from here on instead of
+        being enqueued; the sequence must have run once before (see tfb_ctx_capture_begin)."""
+        check(lib.tfb_ctx_capture_begin(self.handle))
+
+    def capture_end(self) -> "CapturedGraph":
+        h = C.c_void_p()
+        check(lib.tfb_ctx_capture_end(self.handle, C.byref(h)))
+        return CapturedGraph(h, self)
+
     def record_event(self) -> "CompletionEvent":
         h = C.c_void_p()
         check(lib.tfb_event_record(self.handle, C.byref(h)))
@@ -274,6 +284,25 @@ class Context:
 
     def wait_event(self, ev: "CompletionEvent") -> None:
         check(lib.tfb_event_wait(self.handle, ev.handle))
+
+
+class CapturedGraph:
+    """A captured sequence of calls, replayed with `launch()` on the context's stream
+    (tfb_graph_*).  The buffers the captured calls named must stay alive and in place."""
+
+    def __init__(self, handle, ctx):
+        self.handle, self.ctx = handle, ctx
+
+    def launch(self) -> None:
+        check(lib.tfb_graph_launch(self.handle))
+
+    def __del__(self):
+        try:
+            if self.handle:
+                lib.tfb_graph_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
 
 
 class CompletionEvent:

@@ -241,3 +241,60 @@ def test_mma_issue_probe_reports_plausible_clocks(tb):
         with pytest.raises(tb.InvalidArgument):
             ctx.probe_mma_issue_cycles(*bad)
     ctx.synchronize()
+
+
+def test_capture_and_replay_of_a_contraction_sequence(tb, oracle):
+    """tfb_ctx_capture_begin / _end / tfb_graph_launch: a sequence that ran once is captured (nothing runs
+    while capturing), the graph's replays redo it on the buffers' current contents, and calls that
+    make no sense while capturing are refused.  The f64 product is one whose K is split over the
+    CTAs (two launches), the chain step one that uses the in-kernel stream-K reduction."""
+    ctx = tb.Context.get(0)
+    a, b = oracle.normal(9100, (64, 64, 64), np.float64), oracle.normal(9101, (64, 64, 64), np.float64)
+    A, B = tb.Tensor.from_numpy(a), tb.Tensor.from_numpy(b)
+    out = tb.Tensor.zeros([64, 64], dtype=np.float64)
+    tree = tb.ContractionTree.optimize(tb.Subscripts.parse("abc,bcd->ad"), [a.shape, b.shape])
+    chi = 256
+    e0 = oracle.normal(9102, (chi, chi), np.complex128)
+    s0 = oracle.normal(9103, (chi, 2, chi), np.complex128, scale=(1.0 / chi) ** 0.5)
+    E, S = tb.Tensor.from_numpy(e0), tb.Tensor.from_numpy(s0)
+    Sc = S.conj()
+    nxt = tb.Tensor.zeros([chi, chi], dtype=np.complex128)
+    tree3 = tb.ContractionTree.optimize(tb.Subscripts.parse("ab,asc,bsd->cd"), [e0.shape, s0.shape, s0.shape])
+
+    def sequence():
+        tb.einsum_with_plan_into(tree, [A, B], 1.0, 0.0, out)
+        tb.einsum_with_plan_into(tree3, [E, S, Sc], 1.0, 0.0, nxt)
+
+    sequence()  # first use: plans, tables, kernel attributes
+    ctx.synchronize()
+    want_out, want_nxt = out.to_numpy(), nxt.to_numpy()
+    assert oracle.rel_frobenius(want_out, np.einsum("abc,bcd->ad", a, b)) <= 1e-12
+    ctx.memset(out._block.ptr, 0, out._block.nbytes)
+    ctx.memset(nxt._block.ptr, 0, nxt._block.nbytes)
+    ctx.synchronize()
+
+    ctx.capture_begin()
+    with pytest.raises(tb.InvalidArgument):
+        ctx.synchronize()
+    with pytest.raises(tb.InvalidArgument):
+        ctx.capture_begin()
+    sequence()
+    graph = ctx.capture_end()
+    ctx.synchronize()
+    assert not out.to_numpy().any() and not nxt.to_numpy().any()  # capturing ran nothing
+
+    for _ in range(3):  # replays, the stream-K flags of the last run still raised
+        graph.launch()
+    ctx.synchronize()
+    assert np.array_equal(out.to_numpy(), want_out)
+    assert np.array_equal(nxt.to_numpy(), want_nxt)
+
+    # a replay reads the operands as they are now
+    a2 = oracle.normal(9104, (64, 64, 64), np.float64)
+    a2_col = np.ascontiguousarray(a2.ravel(order="F"))  # tensors are stored column-major
+    ctx.h2d(A._block.ptr, a2_col.ctypes.data_as(C.c_void_p), a2_col.nbytes)
+    graph.launch()
+    ctx.synchronize()
+    assert oracle.rel_frobenius(out.to_numpy(), np.einsum("abc,bcd->ad", a2, b)) <= 1e-12
+    with pytest.raises(tb.InvalidArgument):
+        ctx.capture_end()  # not capturing
