@@ -10,6 +10,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/tenferro_b200.h"
@@ -182,6 +183,18 @@ struct ContractProblem {
     int64_t K() const;
     int64_t B() const;
 };
+// The same product with the operands' roles exchanged (C[m,n] = sum_k A B read as
+// C[n,m] = sum_k B A): which operand supplies rows and which columns is a matter of names, since
+// every mode carries its own strides in A, B and C.  A fused multiplier keeps its strides too.
+inline ContractProblem exchange_roles(const ContractProblem& p) {
+    ContractProblem q = p;
+    std::swap(q.m, q.n);
+    std::swap(q.a, q.b);
+    std::swap(q.conj_a, q.conj_b);
+    for (std::vector<Mode>* grp : {&q.batch, &q.m, &q.n, &q.k})
+        for (Mode& md : *grp) std::swap(md.s[0], md.s[1]);
+    return q;
+}
 // CK_DMMA4: the FP64 tensor pipe with FOUR real products per complex one (Complex64 only): slower
 // than the default three-product form, but Re and Im are each accurate to their own size.
 enum ContractKernel { CK_AUTO = 0, CK_SIMT = 1, CK_DMMA = 2, CK_TCGEN05 = 3, CK_DMMA4 = 4 };

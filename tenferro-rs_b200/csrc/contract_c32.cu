@@ -195,8 +195,23 @@ static tfb_status embedded_product(tfb_ctx* ctx, const ContractProblem& p, bool*
     return TFB_OK;
 }
 
+// Floats the set-up kernels of embedded_product write: the 2 x 2 embedding of the first operand
+// (2M x 2K), and a K-major copy of the second (N x 2K) unless it serves in place.
+static double setup_floats(const ContractProblem& p) {
+    const double k2 = 2.0 * (double)p.K() * (double)p.B();
+    return 2.0 * (double)p.M() * k2 + ((b_is_real_view(p) && env_int("TFB_C32_B_IN_PLACE", 1)) ? 0.0 : (double)p.N() * k2);
+}
+
 tfb_status contract_c32_embedded(tfb_ctx* ctx, const ContractProblem& p, bool* declined) {
-    if (!p.mul) return embedded_product(ctx, p, declined);
+    if (!p.mul) {
+        // The embedded operand should be the small one: a tall first operand against a short second
+        // one (M >> N) would spend more time being embedded than the product takes.
+        if (env_int("TFB_C32_EXCHANGE", 1)) {
+            const ContractProblem q = exchange_roles(p);
+            if (setup_floats(q) < 0.6 * setup_floats(p)) return embedded_product(ctx, q, declined);
+        }
+        return embedded_product(ctx, p, declined);
+    }
     // A fused multiplier is a complex product per element, and the real embedding holds the two
     // parts of an element in different rows: the product runs unfused and C is multiplied in
     // place afterwards (no intermediate tensor).  With a beta term the exact kernel takes it.

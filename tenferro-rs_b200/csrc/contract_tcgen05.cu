@@ -85,6 +85,11 @@ struct TcArgs {
     // coordinates (r % cm_e1, r / cm_e1), column n has (n % cn_e1, n / cn_e1).
     int c_tma;
     int cm_e1;
+    // CTA-pair kernel: columns per half of a pair tile (a multiple of 32, at most 128).  A pair tile is
+    // 2 * half_w columns wide and the MMAs have N = 2 * half_w, so an output with up to 256 columns
+    // is ONE tile whose MMAs do no work on padding: half h holds columns [h * half_w, (h + 1) * half_w)
+    // of the tile, in tensor memory as on the output side.
+    int half_w;
 };
 
 // First row (linear index in the group), valid rows and tensor-map coordinates of free-group tile `t`.
@@ -577,7 +582,7 @@ __device__ __forceinline__ PairWork pair_work(const TcArgs& g, int64_t w, uint32
     if (2 * tc.tm + rank >= g.tiles_m) pw.tr_m.valid = 0;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        pw.tr_n[h] = tile_rows(g.b, 2 * tc.tn + h, 128, g.N);
+        pw.tr_n[h] = tile_rows(g.b, 2 * tc.tn + h, g.half_w, g.N);
         if (2 * tc.tn + h >= g.tiles_n) pw.tr_n[h].valid = 0;
     }
     pw.kb_first = pw.split * g.kb_per_split;
@@ -735,7 +740,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // ---------------------------------------------------------------- MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)g.a.mn_major << 15) |
-                                   ((uint32_t)g.b.mn_major << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)g.b.mn_major << 16) | ((uint32_t)((2 * g.half_w) >> 3) << 17) |
                                    ((uint32_t)((2 * kBM) >> 4) << 24);
             const uint32_t a_lbo = g.a.mn_major ? 4096u : 16u, b_lbo = g.b.mn_major ? 4096u : 16u;
             const uint32_t a_sbo = g.a.mn_major ? 512u : 1024u, b_sbo = g.b.mn_major ? 512u : 1024u;
@@ -856,7 +861,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     const int m_in = row_lin % g.cm_e1, m_out = row_lin / g.cm_e1;
                     // box b of the tile: half b / 4, columns 32 (b % 4) .. + 31 of it
                     auto box_valid = [&](int b) { return rows_live && pw.tr_n[b >> 2].valid > (b & 3) * 32; };
-                    auto box_taddr = [&](int b) { return tmem_row + (uint32_t)(buf * BN + b * 32); };
+                    auto box_taddr = [&](int b) { return tmem_row + (uint32_t)(buf * BN + (b >> 2) * g.half_w + (b & 3) * 32); };
                     uint32_t r[2][32];
                     bool in_flight = false;  // the read of box b was issued while box b - 1 was staged
 #pragma unroll
@@ -912,7 +917,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll 1
                     for (int c0 = 0; c0 < 128 && c0 < trn.valid; c0 += 16) {
                         uint32_t r[16];
-                        tc_ld16(tmem_row + (uint32_t)(buf * BN + h * 128 + c0), r);
+                        tc_ld16(tmem_row + (uint32_t)(buf * BN + h * g.half_w + c0), r);
                         float dv[MUL ? 16 : 1];
                         if constexpr (MUL) {
                             // the multiplier's 16 values, all requested before the first store
@@ -955,9 +960,9 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // ---------------------------------------------------------------- split + promote, then epilogue
         const int t = threadIdx.x - 64;
         const int lane_grp = warp & 3;
-        const int half = (warp - 2) >> 2;  // which 128 columns of the tile this warp reads back
-        const int col0 = half * CPW;
-        const uint32_t tmem_mine = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)col0;
+        const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp reads back
+        const int col0 = half * CPW;       // its columns in the split-K partials
+        const uint32_t tmem_mine = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(half * g.half_w);
         const uint32_t leader_split0 = map_to_cta(bar_split(0), 0), leader_promoted0 = map_to_cta(bar_promoted(0), 0);
         float acc[CPW];
         uint32_t it = 0, ch0 = 0;  // k-blocks and chunks handled before this work item
@@ -1167,7 +1172,7 @@ __global__ void __launch_bounds__(256) tf32x3_pair_splitk_finish_kernel(TcArgs g
     {
         const int h = (int)(blockIdx.y * kFinishCols) / 128, j0 = (int)(blockIdx.y * kFinishCols) % 128;
         if (2 * tc.tn + h >= g.tiles_n) return;
-        const TileRows trn = tile_rows(g.b, 2 * tc.tn + h, 128, g.N);
+        const TileRows trn = tile_rows(g.b, 2 * tc.tn + h, g.half_w, g.N);
         const int j_end = min(trn.valid, j0 + kFinishCols);
         for (int j = j0 + threadIdx.x / kBM; j < j_end; j += 256 / kBM) {
             float sum = 0.f;
@@ -1462,7 +1467,8 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
         return (total / o.e1) * o.tiles1;
     };
     g.tiles_m = tiles(g.a, g.M, kBM);  // 128-row tiles; a pair takes two of each
-    g.tiles_n = tiles(g.b, g.N, 128);
+    if (g.half_w == 0) g.half_w = 128;
+    g.tiles_n = tiles(g.b, g.N, g.half_w);
     g.group_m = env_int("TFB_TC_GROUP_M", 8);
     const int64_t pair_tiles = ((g.tiles_m + 1) / 2) * ((g.tiles_n + 1) / 2) * g.B;
     choose_k_split(&g, pair_tiles, ctx->sm_count / 2);
@@ -1627,6 +1633,9 @@ extern "C" tfb_status tfb_probe_tf32_tflops_sustained(tfb_ctx* ctx, double secon
 // the ones derived from p's output strides: the complex path writes into a complex tensor
 // through its f32 view this way; `c_n_modes` / `c_scale` then describe the column offsets in closed form
 // (the N modes of the complex problem, strides times 2).
+// set while contract_tcgen05 runs the same product with its operands' roles exchanged
+static thread_local bool role_exchanged = false;
+
 tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declined, const int64_t* const* c_tables,
                             const std::vector<Mode>* c_n_modes, int c_scale, const std::vector<Mode>* c_m_modes,
                             const std::vector<Mode>* c_batch_modes) {
@@ -1637,16 +1646,42 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     *declined = true;
     if (p.dtype != TFB_F32) return TFB_OK;
     if (env_int("TFB_NO_TCGEN05", 0)) return TFB_OK;
-    const int64_t M = p.M(), N = p.N(), K = p.K();
     // Small problems stay on the SIMT kernel: a 128-row tile would be mostly padding.
-    if (M < 32 || N < 32 || K < 8) return TFB_OK;
-    if (M > INT32_MAX - 256 || N > INT32_MAX - 256 || K > INT32_MAX - 64) return TFB_OK;
-    const int bn = (N >= 256 && env_int("TFB_TC_BN", 256) == 256) ? 256 : 128;
+    if (p.M() < 32 || p.N() < 32 || p.K() < 8) return TFB_OK;
+    if (p.M() > INT32_MAX - 256 || p.N() > INT32_MAX - 256 || p.K() > INT32_MAX - 64) return TFB_OK;
+    // A narrow output: the short free side becomes the COLUMNS of a single tile (below), whose MMAs
+    // then have exactly that many columns.  Which operand supplies rows and which columns is a
+    // matter of names - the product is described by modes - so the operands exchange roles when
+    // the short side is the first one's.
+    if (!role_exchanged && p.M() <= 256 && p.N() > 256 && !p.mul && env_int("TFB_TC_NARROW", 1)) {
+        const ContractProblem q = exchange_roles(p);
+        const int64_t* swapped[3] = {c_tables ? c_tables[0] : nullptr, c_tables ? c_tables[2] : nullptr,
+                                     c_tables ? c_tables[1] : nullptr};
+        role_exchanged = true;
+        // With offset tables from the caller (the Complex32 embedding) the new columns are the caller's
+        // rows, which only its table describes: no closed form for them and no tensor-store map.
+        const tfb_status st = c_tables ? contract_tcgen05(ctx, q, declined, swapped, nullptr, c_scale, nullptr, c_batch_modes)
+                                       : contract_tcgen05(ctx, q, declined);
+        role_exchanged = false;
+        return st;
+    }
+    const int64_t M = p.M(), N = p.N(), K = p.K();
+    // Up to 256 columns in all, one unfused column mode, more rows than one CTA takes: one pair tile
+    // of 2 * half_w columns (see TcArgs::half_w).
+    int half_w = 0;
+    if (N <= 256 && M > kBM && p.n.size() == 1 && env_int("TFB_TC_NARROW", 1) && env_int("TFB_TC_PAIR", 1))
+        half_w = (int)((N + 63) / 64) * 32;
+    const int bn = half_w ? 256 : (N >= 256 && env_int("TFB_TC_BN", 256) == 256) ? 256 : 128;
     // Pairs of CTAs on 256 x 256 tiles when the output has room for them.
-    const bool pair = bn == 256 && M > kBM && env_int("TFB_TC_PAIR", 1);
+    const bool pair = half_w || (bn == 256 && M > kBM && env_int("TFB_TC_PAIR", 1));
     const int rows_b = pair ? 128 : bn;
     OperandMap a = make_operand_map(p, p.m, 0, p.a, kBM);
     OperandMap b = make_operand_map(p, p.n, 1, p.b, rows_b);
+    // half-tiles of half_w columns: the boxes stay 128 rows tall (what lies past a half is not used)
+    auto narrow = [&](OperandMap* o) {
+        if (half_w && o->ok && !o->geom.pack) o->geom.tiles1 = (int)((o->geom.e1 + half_w - 1) / half_w);
+    };
+    narrow(&b);
     std::shared_ptr<ContractTables> t;
     PoolBlock packed_a, packed_b;
     // Large products only: repack an operand that has no tensor map, or whose tiles would be
@@ -1658,7 +1693,7 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
             return (total / o.geom.e1) * o.geom.tiles1 * rows > total + total / 2;
         };
         const int force_pack = env_int("TFB_TC_REPACK", 0);  // bit 0: A, bit 1: B (experiments)
-        const bool pack_a = wasteful(a, M, kBM) || (force_pack & 1), pack_b = wasteful(b, N, rows_b) || (force_pack & 2);
+        const bool pack_a = wasteful(a, M, kBM) || (force_pack & 1), pack_b = wasteful(b, N, half_w ? half_w : rows_b) || (force_pack & 2);
         if (pack_a || pack_b) {
             TFB_TRY(get_tables(ctx, p, &t));
             ContractArgs ca;
@@ -1686,7 +1721,10 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
                 return TFB_OK;
             };
             if (pack_a) TFB_TRY(repack(0, &packed_a, &a));
-            if (pack_b) TFB_TRY(repack(1, &packed_b, &b));
+            if (pack_b) {
+                TFB_TRY(repack(1, &packed_b, &b));
+                narrow(&b);
+            }
         }
     }
     if (!a.ok || !b.ok) return TFB_OK;
@@ -1715,6 +1753,7 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
         g.d_b = t->d_b; g.d_m = t->d_m; g.d_n = t->d_n;
     }
     g.M = M; g.N = N; g.K = K; g.B = p.B();
+    g.half_w = half_w ? half_w : 128;
     g.alpha = (float)p.alpha.re;
     g.beta = (float)p.beta.re;
     // Both operands walk K in the same blocks: 32 at a time inside the inner K mode.

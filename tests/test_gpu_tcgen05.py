@@ -259,3 +259,41 @@ def test_tma_store_epilogue_matches_per_element_stores(tb, oracle, monkeypatch, 
     on, off = _einsum_both_store_paths(tb, monkeypatch, "ijk,kmn->jinm", [a_view, b_view])
     assert np.array_equal(on, off)
     assert oracle.rel_frobenius(on, np.transpose(want, (1, 0, 3, 2))) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(4096, 192, 512), (192, 4096, 512), (2048, 100, 300), (1000, 64, 64), (300, 256, 96),
+                                   (700, 40, 1000), (5000, 32, 2048), (96 * 2, 9216, 640), (256, 300, 128), (260, 250, 8200)])
+@pytest.mark.parametrize("la,lb", [("col", "col"), ("row", "col"), ("col", "row"), ("row", "row")])
+def test_narrow_outputs_are_one_pair_tile_of_their_own_width(tb, oracle, shape, la, lb, monkeypatch):
+    """An output with at most 256 columns (or, with the operands' roles exchanged, at most 256
+    rows) is one CTA-pair tile whose MMAs are exactly as wide as it needs: half-tiles of 32, 64,
+    96 or 128 columns.  Same answers as the full-width tiling and as float64, with alpha, beta
+    and an old output, short and long K (one accumulation chunk, several, split-K)."""
+    m, n, k = shape
+    rng = np.random.default_rng(13 * m + 7 * n + k)
+    a, b = random_array(rng, (m, k), np.float32), random_array(rng, (k, n), np.float32)
+    c0 = random_array(rng, (m, n), np.float32)
+    want = oracle.np_batched_gemm(a, b, 0.75, -0.5, c0)
+    got, name = run(tb, a, b, la, lb, tb.ContractKernel.Auto, 0.75, -0.5, c0)
+    assert name == "tcgen05_tf32x3"
+    assert oracle.rel_frobenius(got, want) <= 1e-5, (shape, la, lb)
+    got0, _ = run(tb, a, b, la, lb, tb.ContractKernel.Auto)  # beta = 0: the tensor-store epilogue where it applies
+    assert oracle.rel_frobenius(got0, oracle.np_batched_gemm(a, b)) <= 1e-5, (shape, la, lb)
+    monkeypatch.setenv("TFB_TC_NARROW", "0")
+    wide, _ = run(tb, a, b, la, lb, tb.ContractKernel.Auto, 0.75, -0.5, c0)
+    assert oracle.rel_frobenius(got, wide.astype(np.float64)) <= 2e-6, (shape, la, lb)
+
+
+@pytest.mark.parametrize("shape", [(96, 4096, 512), (48, 2048, 100), (128, 1024, 4100), (160, 1000, 64), (4096, 96, 512),
+                                   (2048, 48, 100), (3000, 130, 260)])
+def test_complex64_narrow_rows_exchange_roles(tb, oracle, shape):
+    """Complex64 with few rows: the embedded operand (2 M real rows) becomes the column side of the
+    real product; M' = 96, 192, 256 take the narrow tile, 320 does not."""
+    m, n, k = shape
+    rng = np.random.default_rng(17 * m + n + 3 * k)
+    a, b = random_array(rng, (m, k), np.complex64), random_array(rng, (k, n), np.complex64)
+    c0 = random_array(rng, (m, n), np.complex64)
+    ta, tb_, tc = tb.Tensor.from_numpy(a), tb.Tensor.from_numpy(b), tb.Tensor.from_numpy(c0)
+    tb.einsum_into("ik,kj->ij", [ta, tb_], 0.5 - 0.25j, 2.0, tc)
+    want = (0.5 - 0.25j) * (a.astype(np.complex128) @ b.astype(np.complex128)) + 2.0 * c0.astype(np.complex128)
+    assert oracle.rel_frobenius(tc.to_numpy(), want) <= 1e-5, shape
