@@ -1653,7 +1653,8 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
     // then have exactly that many columns.  Which operand supplies rows and which columns is a
     // matter of names - the product is described by modes - so the operands exchange roles when
     // the short side is the first one's.
-    if (!role_exchanged && p.M() <= 256 && p.N() > 256 && !p.mul && env_int("TFB_TC_NARROW", 1)) {
+    if (!role_exchanged && p.M() <= 256 && p.N() > 256 && p.m.size() == 1 && !p.mul && env_int("TFB_TC_NARROW", 1) &&
+        env_int("TFB_TC_PAIR", 1)) {
         const ContractProblem q = exchange_roles(p);
         const int64_t* swapped[3] = {c_tables ? c_tables[0] : nullptr, c_tables ? c_tables[2] : nullptr,
                                      c_tables ? c_tables[1] : nullptr};
