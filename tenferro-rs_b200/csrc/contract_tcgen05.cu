@@ -154,6 +154,56 @@ __device__ __forceinline__ float remainder_rounded(float a) {
     return __uint_as_float(__float_as_uint(r) + 0x1000u);
 }
 
+// a - trunc_tf32(a) without the rounding step: the exact remainder, to be rounded to bf16.
+__device__ __forceinline__ float remainder_exact(float a) {
+    return a - __uint_as_float(__float_as_uint(a) & 0xffffe000u);
+}
+// {lo, hi} as two bf16 in one register (lo in the lower half), round to nearest even.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// BF16C (short-K variant of the pair kernel, both operands K-major): the two correction terms of
+// 3xTF32 as ONE bf16 MMA of K = 16 per 8-deep k-step.  It adds remainder(a) b + a remainder(b) with
+// all four rounded to bf16: the remainders are 2^-10 of the operands and bf16 rounds to 2^-9
+// relative, so the term is wrong by 2^-19 of the product at worst - the size of what 3xTF32 itself
+// leaves out - for two MMAs' worth of tensor-pipe time per k-step instead of three.  A 16-deep
+// bf16 k-step is 32 bytes per row, as an 8-deep TF32 one: the correction tiles have the raw
+// tiles' size, layout and descriptors.  Which of the MMA's sixteen K slots holds what is free as
+// long as both operands agree, and the order is chosen so that ONE 16-byte chunk of a raw tile
+// (four consecutive k of a row) becomes ONE 16-byte unit of the correction tile at the same place:
+// slots 0-3 and 8-11 hold the first kind of value for k 0-3 and 4-7 of the k-step, slots 4-7 and
+// 12-15 the second kind, the kinds being (remainder, value) in A and (value, remainder) in B.
+// (The long-K variant keeps three TF32 MMAs: its converter warps also carry the running sums and
+// have no registers left for this form's loads in flight; and MN-major tiles would change shape.)
+template <bool IS_B>
+__device__ __forceinline__ void store_unit_bf16(char* out, const float4& v) {
+    const uint32_t b0 = pack_bf16x2(v.x, v.y), b1 = pack_bf16x2(v.z, v.w);
+    const uint32_t s0 = pack_bf16x2(remainder_exact(v.x), remainder_exact(v.y));
+    const uint32_t s1 = pack_bf16x2(remainder_exact(v.z), remainder_exact(v.w));
+    *reinterpret_cast<uint4*>(out) = IS_B ? make_uint4(b0, b1, s0, s1) : make_uint4(s0, s1, b0, b1);
+}
+// Both correction tiles (16 KB each, B behind A) of one stage by NTHREADS threads, in rounds of
+// four chunks of each operand with the eight loads of a round issued first.
+template <int NTHREADS>
+__device__ __forceinline__ void convert_stage_bf16(const char* raw, char* out, int t) {
+    constexpr int ROUNDS = 1024 / NTHREADS / 4;
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        float4 va[4], vb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) va[i] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vb[i] = *reinterpret_cast<const float4*>(raw + 16384 + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) store_unit_bf16<false>(out + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u, va[i]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) store_unit_bf16<true>(out + 16384 + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u, vb[i]);
+    }
+}
+
 constexpr int kChunk = 8;           // k-blocks accumulated inside TMEM before promotion (K = 256)
 constexpr int kSplitThreads = 256;  // warps 2..9
 
@@ -604,13 +654,14 @@ __device__ __forceinline__ int pair_num_kb(const TcArgs& g, int64_t w) {
 // half only drain finished accumulators to the output (tcgen05.ld -> global stores).  Stores that
 // wait for the memory system no longer hold up the conversion the tensor cores are waiting for:
 // a short-K product writes its output at DRAM speed WHILE the next tiles are multiplied.
-template <bool MUL, bool SHORTK>
+template <bool MUL, bool SHORTK, bool BF16C>
 // (Ten warps sit three to a scheduler partition of 16 K registers: 168 registers per thread is the
 // most the launch bounds allow, and what the general instantiations use.)
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + kSplitThreads, 1)
 contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const __grid_constant__ CUtensorMap map_c, TcArgs g) {
     using Cfg = PairCfg;
+    static_assert(!BF16C || SHORTK, "the bf16 corrections exist in the short-K variant only");
     constexpr int STAGES = Cfg::STAGES, BN = Cfg::BN, CPW = Cfg::COLS_PER_WARP;
     extern __shared__ char smem_raw[];
     // Both CTAs must lay their rings out identically: descriptors and barrier offsets are
@@ -781,8 +832,14 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 }
 #pragma unroll
                 for (int ks = 0; ks < kBK / 8; ++ks) {
-                    tc_mma_tf32_pair(tmem_d, da_small, db_big, idesc, !(chunk_first && ks == 0));
-                    tc_mma_tf32_pair(tmem_d, da_big, db_small, idesc, 1);
+                    if constexpr (BF16C) {
+                        // bf16 x bf16 -> f32 on the correction tiles (K-major, the raw tiles' descriptors)
+                        tc_mma_f16_pair(tmem_d, da_small, db_small, (idesc & ~((7u << 7) | (7u << 10))) | (1u << 7) | (1u << 10),
+                                        !(chunk_first && ks == 0));
+                    } else {
+                        tc_mma_tf32_pair(tmem_d, da_small, db_big, idesc, !(chunk_first && ks == 0));
+                        tc_mma_tf32_pair(tmem_d, da_big, db_small, idesc, 1);
+                    }
                     tc_mma_tf32_pair(tmem_d, da_big, db_big, idesc, 1);
                     da_big += a_inc;
                     da_small += a_inc;
@@ -816,15 +873,20 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
                     char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
                     constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
+                    if constexpr (BF16C) {
+                        static_assert(Cfg::A_BYTES == 16384 && Cfg::B_BYTES == 16384, "convert_stage_bf16 is written for 16 KB tiles");
+                        convert_stage_bf16<kConvThreads>(big, small, t);
+                    } else {
 #pragma unroll 4
-                    for (int c = t; c < CHUNKS; c += kConvThreads) {
-                        const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
-                        float4 sm;
-                        sm.x = remainder_rounded(v.x);
-                        sm.y = remainder_rounded(v.y);
-                        sm.z = remainder_rounded(v.z);
-                        sm.w = remainder_rounded(v.w);
-                        *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
+                        for (int c = t; c < CHUNKS; c += kConvThreads) {
+                            const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
+                            float4 sm;
+                            sm.x = remainder_rounded(v.x);
+                            sm.y = remainder_rounded(v.y);
+                            sm.z = remainder_rounded(v.z);
+                            sm.w = remainder_rounded(v.w);
+                            *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
+                        }
                     }
                     fence_async_smem();
                     __syncwarp();
@@ -1449,14 +1511,16 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!configured[ctx->device]) {
-            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<false, false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<true, false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<false, true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-            TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<true, true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+#define TFB_PAIR_SMEM(MUL_, SHORT_, C_)                                                                    \
+    TFB_CUDA(cudaFuncSetAttribute(contract_tf32x3_pair_kernel<MUL_, SHORT_, C_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                  Cfg::SMEM_BYTES))
+            TFB_PAIR_SMEM(false, false, false);
+            TFB_PAIR_SMEM(true, false, false);
+            TFB_PAIR_SMEM(false, true, false);
+            TFB_PAIR_SMEM(true, true, false);
+            TFB_PAIR_SMEM(false, true, true);
+            TFB_PAIR_SMEM(true, true, true);
+#undef TFB_PAIR_SMEM
             configured[ctx->device] = true;
         }
     }
@@ -1490,14 +1554,22 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
         // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
         // short K, one accumulation chunk per tile: the variant with dedicated drain warps
         const bool short_k = !via_partials && g.num_kb <= kChunk && env_int("TFB_TC_SHORTK", 1);
-        if (g.mul && short_k)
-            contract_tf32x3_pair_kernel<true, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
-        else if (g.mul)
-            contract_tf32x3_pair_kernel<true, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
-        else if (short_k)
-            contract_tf32x3_pair_kernel<false, true><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
-        else
-            contract_tf32x3_pair_kernel<false, false><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, mc, g);
+        // short K, both operands K-major, at least six k-blocks: the two correction terms of 3xTF32 as one
+        // bf16 MMA (see convert_stage_bf16); with fewer k-blocks the tile's start and end dominate
+        const bool bf16c = short_k && !g.a.mn_major && !g.b.mn_major && g.num_kb >= 6 && env_int("TFB_TC_BF16_CORRECTIONS", 1);
+#define TFB_PAIR_LAUNCH(MUL_, SHORT_, C_)                                                                                   \
+    contract_tf32x3_pair_kernel<MUL_, SHORT_, C_><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, \
+                                                                                                                       mc, g)
+        if (g.mul && short_k) {
+            if (bf16c) TFB_PAIR_LAUNCH(true, true, true); else TFB_PAIR_LAUNCH(true, true, false);
+        } else if (g.mul) {
+            TFB_PAIR_LAUNCH(true, false, false);
+        } else if (short_k) {
+            if (bf16c) TFB_PAIR_LAUNCH(false, true, true); else TFB_PAIR_LAUNCH(false, true, false);
+        } else {
+            TFB_PAIR_LAUNCH(false, false, false);
+        }
+#undef TFB_PAIR_LAUNCH
         TFB_CUDA(cudaGetLastError());
     }
     if (via_partials) {

@@ -95,6 +95,58 @@ def test_short_k_products_drain_through_dedicated_warps(tb, oracle, shape, beta,
     assert oracle.rel_frobenius(got, other) <= 2e-6
 
 
+@pytest.mark.parametrize("shape,beta", [((2048, 2304, 256), 0.0), ((1100, 900, 248), 0.5), ((2, 640, 768, 192), 0.0),
+                                        ((512, 512, 200), -1.0)])
+@pytest.mark.parametrize("spread", [0, 12], ids=["N(0,1)", "magnitudes over 2^24"])
+def test_short_k_k_major_products_take_bf16_corrections(tb, oracle, shape, beta, spread, monkeypatch):
+    """K of 192 to 256 with both operands K-major: the two correction terms of 3xTF32 run as one
+    bf16 product of the remainders and the values.  Same bar against float64 as the three-TF32
+    form, which TFB_TC_BF16_CORRECTIONS=0 brings back, and the two agree to rounding - also when the
+    operands' magnitudes spread over 2^24, where a correction term rounded too early would show."""
+    *batch, m, n, k = shape
+    rng = np.random.default_rng(m + 2 * n + 3 * k + spread)
+    a, b = random_array(rng, (*batch, m, k), np.float32), random_array(rng, (*batch, k, n), np.float32)
+    if spread:
+        a = (a * np.exp2(rng.integers(-spread, spread + 1, a.shape))).astype(np.float32)
+        b = (b * np.exp2(rng.integers(-spread, spread + 1, b.shape))).astype(np.float32)
+    c0 = random_array(rng, (*batch, m, n), np.float32)
+
+    def product():
+        if not batch:
+            return run(tb, a, b, "row", "col", tb.ContractKernel.Auto, 1.0, beta, c0.copy())
+        # [batch, i, k] and [batch, j, k], both with k next to each other in memory and the batch outermost
+        bt = np.ascontiguousarray(np.swapaxes(b, -1, -2))
+        plan = tb.CudaBackend.plan(tb.PrimDescriptor.Contract([0, 1, 2], [0, 3, 2], [0, 1, 3]), [a.shape, bt.shape, c0.shape],
+                                   np.float32)
+        out = tb.Tensor.from_numpy(c0.copy())
+        tb.CudaBackend.execute(plan, 1.0, [Strided(a, rng, "row").to_device(tb), Strided(bt, rng, "row").to_device(tb)], beta, out)
+        return out.to_numpy(), plan.kernel_name
+
+    got, name = product()
+    assert name == "tcgen05_tf32x3"
+    want = oracle.np_batched_gemm(a, b, 1.0, beta, c0)
+    err = oracle.rel_frobenius(got, want)
+    assert err <= 1e-5, err
+    monkeypatch.setenv("TFB_TC_BF16_CORRECTIONS", "0")
+    other, _ = product()
+    err3 = oracle.rel_frobenius(other, want)
+    assert err3 <= 1e-5, err3
+    assert err <= 2 * err3 + 1e-6, (err, err3)
+    assert oracle.rel_frobenius(got, other) <= 3e-6
+    assert not np.array_equal(got, other)  # the switch does select another form of the corrections
+
+
+def test_bf16_corrections_keep_exact_products_exact(tb, oracle):
+    """Operands that TF32 holds exactly (small integers) have zero remainders: the correction
+    product adds nothing and the sums come out exact."""
+    rng = np.random.default_rng(5)
+    a = rng.integers(-8, 9, (768, 256)).astype(np.float32)
+    b = rng.integers(-8, 9, (256, 1024)).astype(np.float32)
+    got, name = run(tb, a, b, "row", "col", tb.ContractKernel.Auto)
+    assert name == "tcgen05_tf32x3"
+    assert np.array_equal(got, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+
+
 def test_short_k_product_into_an_output_without_common_column_stride(tb, oracle):
     """Three free modes on the N side: the drain warps take the column offsets from the table."""
     rng = np.random.default_rng(77)
