@@ -1167,21 +1167,34 @@ def main():
         # TF32 figure).  Two denominators: the burst rate of a cool GPU, and the rate the probe
         # sustains when launched back to back for seconds under the board's power limit - the one
         # that applies to a kernel timed inside a long step, as here.
-        burst = max(wl["tf32_cold"], ctx.probe_tf32_tflops()) / 3.0
-        sustained = None
+        #
+        # With the corrections as one bf16 MMA (the library's default, TFB_TC_BF16_CORRECTIONS) a k-step
+        # costs the tensor pipe TWO MMAs' time - a bf16 MMA of K = 16 takes what a TF32 MMA of K = 8
+        # takes - so the ceiling is HALF the TF32 rate and the fractions are quoted against that;
+        # `frac_of_three_mma_form` is the same figure against the third, for comparison with numbers
+        # taken before the bf16 form existed.
+        mmas = 2.0 if int(os.environ.get("TFB_TC_BF16_CORRECTIONS", "1") or 0) != 0 else 3.0
+        burst_tf32 = max(wl["tf32_cold"], ctx.probe_tf32_tflops())
+        burst = burst_tf32 / mmas
+        sustained_tf32 = None
         if args.sustained_seconds > 0 and rank == 0:
-            sustained = ctx.probe_tf32_tflops_sustained(args.sustained_seconds) / 3.0
+            sustained_tf32 = ctx.probe_tf32_tflops_sustained(args.sustained_seconds)
+        sustained = sustained_tf32 / mmas if sustained_tf32 else None
         peak = sustained or burst
+        share = "half" if mmas == 2.0 else "one third"
         roofline.update({
             "peak": peak, "frac": (achieved / peak) if achieved else None,
             "peak_burst": burst, "frac_burst": (achieved / burst) if achieved else None,
             "peak_sustained": sustained, "frac_sustained": (achieved / sustained) if (achieved and sustained) else None,
-            "peak_source": ("one third of the dense TF32 rate of the library's tcgen05 probe on this GPU: `peak` is the "
+            "mma_per_k_step": int(mmas),
+            "frac_of_three_mma_form": (achieved / ((sustained_tf32 or burst_tf32) / 3.0)) if achieved else None,
+            "peak_source": (f"{share} of the dense TF32 rate of the library's tcgen05 probe on this GPU ({int(mmas)} MMAs' time per "
+                            "k-step): `peak` is the "
                             f"sustained figure (probe launched back to back for {args.sustained_seconds:g} s, rate of "
                             "the last quarter), `peak_burst` the larger of a single probe before and one after the run")
             if sustained else
-            ("one third of the dense TF32 rate of the library's tcgen05 probe on this GPU (burst: the larger of a "
-             "probe before and one after the run)")})
+            (f"{share} of the dense TF32 rate of the library's tcgen05 probe on this GPU ({int(mmas)} MMAs' time per k-step; "
+             "burst: the larger of a probe before and one after the run)")})
     else:
         peak = wl["peak"]()
         roofline.update({"peak": peak, "frac": (achieved / peak) if (achieved and peak) else None,

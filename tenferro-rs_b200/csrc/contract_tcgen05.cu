@@ -165,43 +165,107 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return r;
 }
 
-// BF16C (short-K variant of the pair kernel, both operands K-major): the two correction terms of
-// 3xTF32 as ONE bf16 MMA of K = 16 per 8-deep k-step.  It adds remainder(a) b + a remainder(b) with
-// all four rounded to bf16: the remainders are 2^-10 of the operands and bf16 rounds to 2^-9
-// relative, so the term is wrong by 2^-19 of the product at worst - the size of what 3xTF32 itself
-// leaves out - for two MMAs' worth of tensor-pipe time per k-step instead of three.  A 16-deep
-// bf16 k-step is 32 bytes per row, as an 8-deep TF32 one: the correction tiles have the raw
-// tiles' size, layout and descriptors.  Which of the MMA's sixteen K slots holds what is free as
-// long as both operands agree, and the order is chosen so that ONE 16-byte chunk of a raw tile
-// (four consecutive k of a row) becomes ONE 16-byte unit of the correction tile at the same place:
+// BF16C (the CTA-pair kernel): the two correction terms of 3xTF32 as ONE bf16 MMA of K = 16 per
+// 8-deep k-step.  It adds remainder(a) b + a remainder(b) with all four rounded to bf16: the
+// remainders are 2^-10 of the operands and bf16 rounds to 2^-9 relative, so the term is wrong by
+// 2^-19 of the product at worst - the size of what 3xTF32 itself leaves out - for two MMAs' worth
+// of tensor-pipe time (and power) per k-step instead of three.  A 16-deep bf16 k-step is 32 bytes
+// per row, as an 8-deep TF32 one, so the correction tiles have the raw tiles' size.
+//
+// Which of the MMA's sixteen K slots holds what is free as long as both operands agree, and the
+// order is chosen so that ONE 16-byte chunk of a raw K-major tile (four consecutive k of a row)
+// becomes ONE 16-byte unit of the correction tile at the same place, in the raw tile's layout:
 // slots 0-3 and 8-11 hold the first kind of value for k 0-3 and 4-7 of the k-step, slots 4-7 and
 // 12-15 the second kind, the kinds being (remainder, value) in A and (value, remainder) in B.
-// (The long-K variant keeps three TF32 MMAs: its converter warps also carry the running sums and
-// have no registers left for this form's loads in flight; and MN-major tiles would change shape.)
+// An MN-major tile ([32 k][32 mn] boxes, 32-byte units swizzled by k) becomes [64 k'][64 mn]
+// blocks of 128-byte rows (16-byte units swizzled by k'): a thread takes the eight consecutive mn
+// of one k (one 32-byte unit) and writes one unit into each of the two rows that are that k's slots.
+__device__ __forceinline__ const char* mn_pair_src(const char* raw, uint32_t q) {
+    // eight threads take the same k of two neighbouring boxes: the eight units of one new row
+    const uint32_t box = ((q >> 8) << 1) | ((q >> 2) & 1u), k = (q >> 3) & 31u, a = q & 3u;
+    return raw + (box << 12) + (k << 7) + (a << 5);
+}
 template <bool IS_B>
-__device__ __forceinline__ void store_unit_bf16(char* out, const float4& v) {
+__device__ __forceinline__ void store_unit_kmajor(char* out, uint32_t c, const float4& v) {
     const uint32_t b0 = pack_bf16x2(v.x, v.y), b1 = pack_bf16x2(v.z, v.w);
     const uint32_t s0 = pack_bf16x2(remainder_exact(v.x), remainder_exact(v.y));
     const uint32_t s1 = pack_bf16x2(remainder_exact(v.z), remainder_exact(v.w));
-    *reinterpret_cast<uint4*>(out) = IS_B ? make_uint4(b0, b1, s0, s1) : make_uint4(s0, s1, b0, b1);
+    *reinterpret_cast<uint4*>(out + c * 16u) = IS_B ? make_uint4(b0, b1, s0, s1) : make_uint4(s0, s1, b0, b1);
 }
-// Both correction tiles (16 KB each, B behind A) of one stage by NTHREADS threads, in rounds of
-// four chunks of each operand with the eight loads of a round issued first.
-template <int NTHREADS>
+// v0, v1: the eight consecutive mn of 32-byte unit q, in order
+template <bool IS_B>
+__device__ __forceinline__ void store_units_mnmajor(char* out, uint32_t q, const float4& v0, const float4& v1) {
+    const uint32_t box = ((q >> 8) << 1) | ((q >> 2) & 1u), k = (q >> 3) & 31u, a = q & 3u;
+    const uint4 big = make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v0.z, v0.w), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v1.z, v1.w));
+    const uint4 small = make_uint4(pack_bf16x2(remainder_exact(v0.x), remainder_exact(v0.y)),
+                                   pack_bf16x2(remainder_exact(v0.z), remainder_exact(v0.w)),
+                                   pack_bf16x2(remainder_exact(v1.x), remainder_exact(v1.y)),
+                                   pack_bf16x2(remainder_exact(v1.z), remainder_exact(v1.w)));
+    const uint32_t u = 4u * (box & 1u) + (a ^ (k & 3u));  // the 16-byte unit of these eight mn in the block's row
+    // k's two slots among the sixteen of its k-step: (k & 3) + 8 (k / 4 & 1) and four further on
+    const uint32_t row0 = ((k >> 3) << 4) + (k & 3u) + ((k & 4u) << 1);
+    char* d0 = out + (box >> 1) * 8192u + row0 * 128u + (((u ^ row0) & 7u) << 4);
+    char* d1 = out + (box >> 1) * 8192u + (row0 + 4u) * 128u + (((u ^ (row0 + 4u)) & 7u) << 4);
+    *reinterpret_cast<uint4*>(d0) = IS_B ? big : small;
+    *reinterpret_cast<uint4*>(d1) = IS_B ? small : big;
+}
+// One operand's four 16-byte loads of a round (K-major: four chunks; MN-major: two 32-byte units,
+// read second half first by every other group of four threads so that a quarter-warp's loads
+// cover all banks), and the matching stores.
+template <bool MN, int NTHREADS>
+__device__ __forceinline__ void load_round(const char* raw, int t, int r, uint32_t first, float4 (&v)[4]) {
+    if constexpr (!MN) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const char* src = mn_pair_src(raw, (uint32_t)(t + (2 * r + i) * NTHREADS));
+            v[2 * i] = *reinterpret_cast<const float4*>(src + first);
+            v[2 * i + 1] = *reinterpret_cast<const float4*>(src + (16u - first));
+        }
+    }
+}
+template <bool MN, bool IS_B, int NTHREADS>
+__device__ __forceinline__ void store_round(char* out, int t, int r, uint32_t first, const float4 (&v)[4]) {
+    if constexpr (!MN) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) store_unit_kmajor<IS_B>(out, (uint32_t)(t + (4 * r + i) * NTHREADS), v[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float4 lo = v[2 * i], hi = v[2 * i + 1];
+            if (first) {
+                const float4 tmp = lo;
+                lo = hi;
+                hi = tmp;
+            }
+            store_units_mnmajor<IS_B>(out, (uint32_t)(t + (2 * r + i) * NTHREADS), lo, hi);
+        }
+    }
+}
+// Both correction tiles (16 KB each, B behind A) of one stage by NTHREADS threads (t: this thread's
+// number among them), in rounds of four chunks of each operand with the eight loads of a round
+// issued first.
+template <int NTHREADS, bool A_MN, bool B_MN>
 __device__ __forceinline__ void convert_stage_bf16(const char* raw, char* out, int t) {
     constexpr int ROUNDS = 1024 / NTHREADS / 4;
+    const uint32_t first = ((t >> 2) & 1) ? 16u : 0u;
 #pragma unroll
     for (int r = 0; r < ROUNDS; ++r) {
         float4 va[4], vb[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) va[i] = *reinterpret_cast<const float4*>(raw + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) vb[i] = *reinterpret_cast<const float4*>(raw + 16384 + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) store_unit_bf16<false>(out + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u, va[i]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) store_unit_bf16<true>(out + 16384 + (uint32_t)(t + (4 * r + i) * NTHREADS) * 16u, vb[i]);
+        load_round<A_MN, NTHREADS>(raw, t, r, first, va);
+        load_round<B_MN, NTHREADS>(raw + 16384, t, r, first, vb);
+        store_round<A_MN, false, NTHREADS>(out, t, r, first, va);
+        store_round<B_MN, true, NTHREADS>(out + 16384, t, r, first, vb);
     }
+}
+template <int NTHREADS>
+__device__ __forceinline__ void convert_stage_bf16(const char* raw, char* out, int t, bool a_mn, bool b_mn) {
+    if (!a_mn && !b_mn) convert_stage_bf16<NTHREADS, false, false>(raw, out, t);
+    else if (!a_mn) convert_stage_bf16<NTHREADS, false, true>(raw, out, t);
+    else if (!b_mn) convert_stage_bf16<NTHREADS, true, false>(raw, out, t);
+    else convert_stage_bf16<NTHREADS, true, true>(raw, out, t);
 }
 
 constexpr int kChunk = 8;           // k-blocks accumulated inside TMEM before promotion (K = 256)
@@ -654,14 +718,23 @@ __device__ __forceinline__ int pair_num_kb(const TcArgs& g, int64_t w) {
 // half only drain finished accumulators to the output (tcgen05.ld -> global stores).  Stores that
 // wait for the memory system no longer hold up the conversion the tensor cores are waiting for:
 // a short-K product writes its output at DRAM speed WHILE the next tiles are multiplied.
+constexpr int pair_lead_threads(bool shortk) { return shortk ? 64 : 128; }
+constexpr int pair_threads(bool shortk) { return pair_lead_threads(shortk) + kSplitThreads; }
+constexpr int kLeadRegs = 72, kWorkerRegs = 216;
+static_assert(kLeadRegs + 2 * kWorkerRegs <= 512 && pair_threads(false) * 168 >= 128 * kLeadRegs + 256 * kWorkerRegs,
+              "the registers the workers take are the ones the lead warps gave up");
+
 template <bool MUL, bool SHORTK, bool BF16C>
-// (Ten warps sit three to a scheduler partition of 16 K registers: 168 registers per thread is the
-// most the launch bounds allow, and what the general instantiations use.)
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + kSplitThreads, 1)
+// Registers.  The short-K variant runs ten warps (producer, MMA issuer, eight workers) in the 168
+// registers per thread that three warps to a scheduler partition of 16 K registers leave.  The long-K
+// variant's workers hold a 128-wide row of running sums each and want more: it runs TWELVE warps, the
+// first warpgroup (producer, MMA issuer, two warps without a role) gives its registers up to
+// kLeadRegs per thread and the two worker warpgroups take kWorkerRegs (a partition then holds
+// kLeadRegs + 2 kWorkerRegs <= 512 per lane).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(SHORTK), 1)
 contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const __grid_constant__ CUtensorMap map_c, TcArgs g) {
     using Cfg = PairCfg;
-    static_assert(!BF16C || SHORTK, "the bf16 corrections exist in the short-K variant only");
     constexpr int STAGES = Cfg::STAGES, BN = Cfg::BN, CPW = Cfg::COLS_PER_WARP;
     extern __shared__ char smem_raw[];
     // Both CTAs must lay their rings out identically: descriptors and barrier offsets are
@@ -684,6 +757,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     constexpr int kWarps = kSplitThreads / 32;
+    constexpr int kLead = pair_lead_threads(SHORTK), kLeadWarps = kLead / 32;  // threads and warps before the workers
     // warps per CTA that arrive on the "converted" and on the "accumulator drained" barriers
     constexpr int kRoleWarps = SHORTK ? kWarps / 2 : kWarps;
 
@@ -716,6 +790,8 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     tc_fence_after();
     const uint32_t tmem_base = *tmem_word_ptr;
 
+    if (warp < kLeadWarps) {
+    if constexpr (!SHORTK) reg_release<kLeadRegs>();
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (each CTA its own tiles)
         if (lane == 0) {
@@ -803,9 +879,18 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             // this thread computes between a stage being converted and its first MMA delays the tile.
             const uint64_t da_big0 = smem_desc(ring, a_lbo, a_sbo, a_lay);
             const uint64_t db_big0 = smem_desc(ring + Cfg::A_BYTES, b_lbo, b_sbo, b_lay);
-            const uint64_t da_small0 = smem_desc(ring + Cfg::A_BYTES + Cfg::B_BYTES, a_lbo, a_sbo, a_lay);
-            const uint64_t db_small0 = smem_desc(ring + 2 * Cfg::A_BYTES + Cfg::B_BYTES, b_lbo, b_sbo, b_lay);
-            const uint32_t a_inc = a_step >> 4, b_inc = b_step >> 4;
+            // The second operands: TF32 remainders in the raw tiles' layout, or (BF16C) bf16 correction
+            // tiles - K-major ones in the same layout, MN-major ones as [64 k'][64 mn] blocks 8192
+            // bytes apart with 8-row swizzle atoms 1024 bytes apart, a 16-deep k-step moving 2048 bytes.
+            const uint32_t a2_lbo = BF16C && g.a.mn_major ? 8192u : a_lbo, b2_lbo = BF16C && g.b.mn_major ? 8192u : b_lbo;
+            const uint32_t a2_sbo = BF16C ? 1024u : a_sbo, b2_sbo = BF16C ? 1024u : b_sbo;
+            const uint32_t a2_lay = BF16C ? 2u : a_lay, b2_lay = BF16C ? 2u : b_lay;
+            const uint32_t a2_step = BF16C && g.a.mn_major ? 2048u : a_step, b2_step = BF16C && g.b.mn_major ? 2048u : b_step;
+            const uint64_t da_small0 = smem_desc(ring + Cfg::A_BYTES + Cfg::B_BYTES, a2_lbo, a2_sbo, a2_lay);
+            const uint64_t db_small0 = smem_desc(ring + 2 * Cfg::A_BYTES + Cfg::B_BYTES, b2_lbo, b2_sbo, b2_lay);
+            const uint32_t a_inc = a_step >> 4, b_inc = b_step >> 4, a2_inc = a2_step >> 4, b2_inc = b2_step >> 4;
+            // bf16 x bf16 -> f32, same shape and majors
+            const uint32_t idesc_c = (idesc & ~((7u << 7) | (7u << 10))) | (1u << 7) | (1u << 10);
             int m_stage = 0;
             uint32_t m_parity = 0;
             for (int64_t w = w0; w < n_work; w += wstep) {
@@ -833,18 +918,16 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
                 for (int ks = 0; ks < kBK / 8; ++ks) {
                     if constexpr (BF16C) {
-                        // bf16 x bf16 -> f32 on the correction tiles (K-major, the raw tiles' descriptors)
-                        tc_mma_f16_pair(tmem_d, da_small, db_small, (idesc & ~((7u << 7) | (7u << 10))) | (1u << 7) | (1u << 10),
-                                        !(chunk_first && ks == 0));
+                        tc_mma_f16_pair(tmem_d, da_small, db_small, idesc_c, !(chunk_first && ks == 0));
                     } else {
                         tc_mma_tf32_pair(tmem_d, da_small, db_big, idesc, !(chunk_first && ks == 0));
                         tc_mma_tf32_pair(tmem_d, da_big, db_small, idesc, 1);
                     }
                     tc_mma_tf32_pair(tmem_d, da_big, db_big, idesc, 1);
                     da_big += a_inc;
-                    da_small += a_inc;
+                    da_small += a2_inc;
                     db_big += b_inc;
-                    db_small += b_inc;
+                    db_small += b2_inc;
                 }
                 tc_commit_pair(bar_empty(s));
                 tc_commit_pair(map_to_cta(bar_empty(s), 1));
@@ -856,12 +939,13 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             ch0 += (uint32_t)((num_kb + kChunk - 1) / kChunk);
             }
         }
+    }
     } else if constexpr (SHORTK) {
         const uint32_t leader_split0 = map_to_cta(bar_split(0), 0), leader_promoted0 = map_to_cta(bar_promoted(0), 0);
-        if (warp < 2 + kRoleWarps) {
+        if (warp < kLeadWarps + kRoleWarps) {
             // ------------------------------------------------------------ converters only (warps 2-5)
             constexpr int kConvThreads = kRoleWarps * 32;
-            const int t = threadIdx.x - 64;
+            const int t = threadIdx.x - kLead;
             uint32_t it = 0;
             for (int64_t w = w0; w < n_work; w += wstep) {
                 const int num_kb = pair_num_kb(g, w);
@@ -875,7 +959,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
                     if constexpr (BF16C) {
                         static_assert(Cfg::A_BYTES == 16384 && Cfg::B_BYTES == 16384, "convert_stage_bf16 is written for 16 KB tiles");
-                        convert_stage_bf16<kConvThreads>(big, small, t);
+                        convert_stage_bf16<kConvThreads>(big, small, t, g.a.mn_major != 0, g.b.mn_major != 0);
                     } else {
 #pragma unroll 4
                         for (int c = t; c < CHUNKS; c += kConvThreads) {
@@ -902,7 +986,7 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t tmem_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
             const bool read_c = g.beta != 0.f;
             // TMA-store path: two 2 KB boxes per drain warp, used alternately
-            const int slot0 = (warp - 2 - kRoleWarps) * 2;
+            const int slot0 = (warp - kLeadWarps - kRoleWarps) * 2;
             uint32_t n_boxes = 0;
             uint32_t chunk = 0;
             for (int64_t w = w0; w < n_work; w += wstep, ++chunk) {
@@ -1020,9 +1104,10 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
     } else {
         // ---------------------------------------------------------------- split + promote, then epilogue
-        const int t = threadIdx.x - 64;
+        reg_acquire<kWorkerRegs>();
+        const int t = threadIdx.x - kLead;
         const int lane_grp = warp & 3;
-        const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp reads back
+        const int half = (warp - kLeadWarps) >> 2;  // which half of the tile's columns this warp reads back
         const int col0 = half * CPW;       // its columns in the split-K partials
         const uint32_t tmem_mine = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(half * g.half_w);
         const uint32_t leader_split0 = map_to_cta(bar_split(0), 0), leader_promoted0 = map_to_cta(bar_promoted(0), 0);
@@ -1035,12 +1120,12 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         // later); what is left is flushed before that promotion.
         constexpr int kSlices = 6;
         // With the TMA-store epilogue the pending tile leaves in kTmaSlices boxes of kBoxCols columns,
-        // staged in this warp's box of shared memory (warp - 2 = slot) and written by one bulk store each.
+        // staged in this warp's box of shared memory (worker number = slot) and written by one bulk store each.
         constexpr int kTmaSlices = CPW / kBoxCols;
         const bool c_tma = !MUL && g.c_tma;
         const int n_slices = c_tma ? kTmaSlices : kSlices;
-        float* const my_box = out_stage_ptr + (warp - 2) * (kBoxBytes / 4) + lane;
-        const uint32_t my_box_addr = out_stage + (uint32_t)((warp - 2) * kBoxBytes);
+        float* const my_box = out_stage_ptr + (warp - kLeadWarps) * (kBoxBytes / 4) + lane;
+        const uint32_t my_box_addr = out_stage + (uint32_t)((warp - kLeadWarps) * kBoxBytes);
         int pend_m_in = 0, pend_m_out = 0, pend_batch = 0;  // tensor-map coordinates of the pending tile's rows
         float* pend_row = nullptr;   // &C[row, 0] of the pending tile, nullptr: nothing pending
         const float* pend_drow = nullptr;  // the fused multiplier's row of that tile, nullptr: no multiplier
@@ -1116,16 +1201,20 @@ contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             char* big = smem + (size_t)s * Cfg::STAGE_BYTES;
             char* small = big + Cfg::A_BYTES + Cfg::B_BYTES;
             constexpr int CHUNKS = (Cfg::A_BYTES + Cfg::B_BYTES) / 16;
+            if constexpr (BF16C) {
+                convert_stage_bf16<kSplitThreads>(big, small, t, g.a.mn_major != 0, g.b.mn_major != 0);
+            } else {
 #pragma unroll 8
-            for (int c = t; c < CHUNKS; c += kSplitThreads) {
-                const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
-                float4 sm;
-                // raw tile = truncated big operand; remainder exact, rounded to tf32
-                sm.x = remainder_rounded(v.x);
-                sm.y = remainder_rounded(v.y);
-                sm.z = remainder_rounded(v.z);
-                sm.w = remainder_rounded(v.w);
-                *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
+                for (int c = t; c < CHUNKS; c += kSplitThreads) {
+                    const float4 v = *reinterpret_cast<const float4*>(big + (size_t)c * 16);
+                    float4 sm;
+                    // raw tile = truncated big operand; remainder exact, rounded to tf32
+                    sm.x = remainder_rounded(v.x);
+                    sm.y = remainder_rounded(v.y);
+                    sm.z = remainder_rounded(v.z);
+                    sm.w = remainder_rounded(v.w);
+                    *reinterpret_cast<float4*>(small + (size_t)c * 16) = sm;
+                }
             }
             fence_async_smem();
             __syncwarp();
@@ -1520,6 +1609,8 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
             TFB_PAIR_SMEM(true, true, false);
             TFB_PAIR_SMEM(false, true, true);
             TFB_PAIR_SMEM(true, true, true);
+            TFB_PAIR_SMEM(false, false, true);
+            TFB_PAIR_SMEM(true, false, true);
 #undef TFB_PAIR_SMEM
             configured[ctx->device] = true;
         }
@@ -1554,21 +1645,22 @@ tfb_status launch_tc_pair(tfb_ctx* ctx, const OperandMap& a, const OperandMap& b
         // the cluster shape (2, 1, 1) is a compile-time attribute of the kernel
         // short K, one accumulation chunk per tile: the variant with dedicated drain warps
         const bool short_k = !via_partials && g.num_kb <= kChunk && env_int("TFB_TC_SHORTK", 1);
-        // short K, both operands K-major, at least six k-blocks: the two correction terms of 3xTF32 as one
-        // bf16 MMA (see convert_stage_bf16); with fewer k-blocks the tile's start and end dominate
-        const bool bf16c = short_k && !g.a.mn_major && !g.b.mn_major && g.num_kb >= 6 && env_int("TFB_TC_BF16_CORRECTIONS", 1);
+        // the two correction terms of 3xTF32 as one bf16 MMA (see convert_stage_bf16); a short-K tile of fewer
+        // than six k-blocks is dominated by its start and end and keeps the three TF32 MMAs
+        const bool bf16c = env_int("TFB_TC_BF16_CORRECTIONS", 1) != 0 && (!short_k || g.num_kb >= 6);
 #define TFB_PAIR_LAUNCH(MUL_, SHORT_, C_)                                                                                   \
-    contract_tf32x3_pair_kernel<MUL_, SHORT_, C_><<<(unsigned)grid, 64 + kSplitThreads, Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, \
+    contract_tf32x3_pair_kernel<MUL_, SHORT_, C_><<<(unsigned)grid, pair_threads(SHORT_), Cfg::SMEM_BYTES, ctx->stream>>>(a.map, b.map, \
                                                                                                                        mc, g)
-        if (g.mul && short_k) {
-            if (bf16c) TFB_PAIR_LAUNCH(true, true, true); else TFB_PAIR_LAUNCH(true, true, false);
-        } else if (g.mul) {
-            TFB_PAIR_LAUNCH(true, false, false);
-        } else if (short_k) {
-            if (bf16c) TFB_PAIR_LAUNCH(false, true, true); else TFB_PAIR_LAUNCH(false, true, false);
-        } else {
-            TFB_PAIR_LAUNCH(false, false, false);
-        }
+#define TFB_PAIR_LAUNCH2(MUL_, SHORT_)                                                                                      \
+    do {                                                                                                                    \
+        if (bf16c) TFB_PAIR_LAUNCH(MUL_, SHORT_, true);                                                                     \
+        else TFB_PAIR_LAUNCH(MUL_, SHORT_, false);                                                                          \
+    } while (0)
+        if (g.mul && short_k) TFB_PAIR_LAUNCH2(true, true);
+        else if (g.mul) TFB_PAIR_LAUNCH2(true, false);
+        else if (short_k) TFB_PAIR_LAUNCH2(false, true);
+        else TFB_PAIR_LAUNCH2(false, false);
+#undef TFB_PAIR_LAUNCH2
 #undef TFB_PAIR_LAUNCH
         TFB_CUDA(cudaGetLastError());
     }

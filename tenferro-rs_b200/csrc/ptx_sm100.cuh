@@ -193,6 +193,17 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_des
 }
 
 // The same with 16-bit operands (bf16 or f16, chosen by the instruction descriptor), K = 16 per MMA.
+// Moves registers between the warps of a CTA: every warp of a warpgroup (four consecutive warps) gives up
+// registers down to N per thread, or waits until it can take up to N.  N is a multiple of 8 in 24..256.
+template <int N>
+__device__ __forceinline__ void reg_release() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_acquire() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 __device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                 uint32_t accumulate) {
     asm volatile(

@@ -96,14 +96,20 @@ def test_short_k_products_drain_through_dedicated_warps(tb, oracle, shape, beta,
 
 
 @pytest.mark.parametrize("shape,beta", [((2048, 2304, 256), 0.0), ((1100, 900, 248), 0.5), ((2, 640, 768, 192), 0.0),
-                                        ((512, 512, 200), -1.0)])
+                                        ((512, 512, 200), -1.0), ((768, 1024, 1024), 0.0), ((640, 520, 2100), 0.25),
+                                        ((200, 300, 9216), 0.0)])
+@pytest.mark.parametrize("la,lb", [("row", "col"), ("col", "col"), ("row", "row"), ("col", "row")])
 @pytest.mark.parametrize("spread", [0, 12], ids=["N(0,1)", "magnitudes over 2^24"])
-def test_short_k_k_major_products_take_bf16_corrections(tb, oracle, shape, beta, spread, monkeypatch):
-    """K of 192 to 256 with both operands K-major: the two correction terms of 3xTF32 run as one
-    bf16 product of the remainders and the values.  Same bar against float64 as the three-TF32
-    form, which TFB_TC_BF16_CORRECTIONS=0 brings back, and the two agree to rounding - also when the
-    operands' magnitudes spread over 2^24, where a correction term rounded too early would show."""
+def test_corrections_as_one_bf16_product(tb, oracle, shape, beta, la, lb, spread, monkeypatch):
+    """The CTA-pair kernel runs the two correction terms of 3xTF32 as one bf16 product of the
+    remainders and the values: short K (one accumulation chunk, 192 to 256), long K (promotions,
+    ragged last k-block) and split K, every operand-major combination, a batch.  Same bar against
+    float64 as the three-TF32 form, which TFB_TC_BF16_CORRECTIONS=0 brings back, and the two agree
+    to rounding - also when the operands' magnitudes spread over 2^24, where a correction term
+    rounded too early would show."""
     *batch, m, n, k = shape
+    if batch and (la, lb) != ("row", "col"):
+        pytest.skip("the batched case is built with both operands K-major")
     rng = np.random.default_rng(m + 2 * n + 3 * k + spread)
     a, b = random_array(rng, (*batch, m, k), np.float32), random_array(rng, (*batch, k, n), np.float32)
     if spread:
@@ -113,7 +119,7 @@ def test_short_k_k_major_products_take_bf16_corrections(tb, oracle, shape, beta,
 
     def product():
         if not batch:
-            return run(tb, a, b, "row", "col", tb.ContractKernel.Auto, 1.0, beta, c0.copy())
+            return run(tb, a, b, la, lb, tb.ContractKernel.Auto, 1.0, beta, c0.copy())
         # [batch, i, k] and [batch, j, k], both with k next to each other in memory and the batch outermost
         bt = np.ascontiguousarray(np.swapaxes(b, -1, -2))
         plan = tb.CudaBackend.plan(tb.PrimDescriptor.Contract([0, 1, 2], [0, 3, 2], [0, 1, 3]), [a.shape, bt.shape, c0.shape],
@@ -136,15 +142,17 @@ def test_short_k_k_major_products_take_bf16_corrections(tb, oracle, shape, beta,
     assert not np.array_equal(got, other)  # the switch does select another form of the corrections
 
 
-def test_bf16_corrections_keep_exact_products_exact(tb, oracle):
+@pytest.mark.parametrize("k", [256, 4096])
+def test_bf16_corrections_keep_exact_products_exact(tb, oracle, k):
     """Operands that TF32 holds exactly (small integers) have zero remainders: the correction
     product adds nothing and the sums come out exact."""
     rng = np.random.default_rng(5)
-    a = rng.integers(-8, 9, (768, 256)).astype(np.float32)
-    b = rng.integers(-8, 9, (256, 1024)).astype(np.float32)
-    got, name = run(tb, a, b, "row", "col", tb.ContractKernel.Auto)
-    assert name == "tcgen05_tf32x3"
-    assert np.array_equal(got, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+    a = rng.integers(-8, 9, (768, k)).astype(np.float32)
+    b = rng.integers(-8, 9, (k, 1024)).astype(np.float32)
+    for la, lb in (("row", "col"), ("col", "row")):
+        got, name = run(tb, a, b, la, lb, tb.ContractKernel.Auto)
+        assert name == "tcgen05_tf32x3"
+        assert np.array_equal(got, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
 
 
 def test_short_k_product_into_an_output_without_common_column_stride(tb, oracle):
