@@ -711,6 +711,19 @@ __device__ __forceinline__ int pair_num_kb(const TcArgs& g, int64_t w) {
     return min(g.kb_per_split, g.num_kb - split * g.kb_per_split);
 }
 
+// Threads of the pair kernel: the lead warps (producer, MMA issuer and, in the long-K variant, two
+// warps that only hand their registers over) and eight worker warps.
+constexpr int pair_lead_threads(bool shortk) { return shortk ? 64 : 128; }
+constexpr int pair_threads(bool shortk) { return pair_lead_threads(shortk) + kSplitThreads; }
+// Registers.  The short-K variant runs ten warps in the 168 registers per thread that three warps
+// to a scheduler partition of 16 K registers leave.  The long-K variant's workers hold a 128-wide
+// row of running sums each and want more: it runs TWELVE warps at 168, the first warpgroup gives
+// its registers up to kLeadRegs per thread and the two worker warpgroups take kWorkerRegs (a
+// partition then holds kLeadRegs + 2 kWorkerRegs of its 512 per lane).
+constexpr int kLeadRegs = 72, kWorkerRegs = 216;
+static_assert(kLeadRegs + 2 * kWorkerRegs <= 512 && pair_threads(false) * 168 >= 128 * kLeadRegs + 256 * kWorkerRegs,
+              "the registers the workers take are the ones the lead warps gave up");
+
 // MUL: the launch carries a fused multiplier (g.mul != nullptr).  A separate instantiation keeps the
 // multiplier's registers out of the plain kernel.
 // SHORTK: every work item fits one TMEM accumulation chunk (K <= kChunk k-blocks, no split-K), so
@@ -718,19 +731,9 @@ __device__ __forceinline__ int pair_num_kb(const TcArgs& g, int64_t w) {
 // half only drain finished accumulators to the output (tcgen05.ld -> global stores).  Stores that
 // wait for the memory system no longer hold up the conversion the tensor cores are waiting for:
 // a short-K product writes its output at DRAM speed WHILE the next tiles are multiplied.
-constexpr int pair_lead_threads(bool shortk) { return shortk ? 64 : 128; }
-constexpr int pair_threads(bool shortk) { return pair_lead_threads(shortk) + kSplitThreads; }
-constexpr int kLeadRegs = 72, kWorkerRegs = 216;
-static_assert(kLeadRegs + 2 * kWorkerRegs <= 512 && pair_threads(false) * 168 >= 128 * kLeadRegs + 256 * kWorkerRegs,
-              "the registers the workers take are the ones the lead warps gave up");
-
+// BF16C: the two correction terms of a k-step as one bf16 MMA on correction tiles (see
+// convert_stage_bf16) instead of two TF32 MMAs on remainder tiles.
 template <bool MUL, bool SHORTK, bool BF16C>
-// Registers.  The short-K variant runs ten warps (producer, MMA issuer, eight workers) in the 168
-// registers per thread that three warps to a scheduler partition of 16 K registers leave.  The long-K
-// variant's workers hold a 128-wide row of running sums each and want more: it runs TWELVE warps, the
-// first warpgroup (producer, MMA issuer, two warps without a role) gives its registers up to
-// kLeadRegs per thread and the two worker warpgroups take kWorkerRegs (a partition then holds
-// kLeadRegs + 2 kWorkerRegs <= 512 per lane).
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(SHORTK), 1)
 contract_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const __grid_constant__ CUtensorMap map_c, TcArgs g) {
