@@ -1355,26 +1355,40 @@ struct RepackArgs {
     int src_kfast;
     float* dst;
 };
+constexpr int kRepackTile = 64;
 __global__ void __launch_bounds__(256) repack_kmajor_kernel(RepackArgs g) {
-    __shared__ float tile[32][33];
-    const int64_t tiles_r = (g.rows + 31) / 32, tiles_k = (g.Kp + 31) / 32;
+    constexpr int T = kRepackTile;
+    __shared__ float tile[T][T + 1];
+    const int64_t tiles_r = (g.rows + T - 1) / T, tiles_k = (g.Kp + T - 1) / T;
     const int64_t n_tiles = tiles_r * tiles_k * g.B;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const int tx = threadIdx.x & (T - 1), ty = threadIdx.x / T;  // 64 x 4
+    constexpr int kPer = T * T / 256;                            // elements per thread and tile
     for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
         const int64_t tr = t % tiles_r, rest = t / tiles_r, tk = rest % tiles_k, b = rest / tiles_k;
-        const int64_t r0 = tr * 32, k0 = tk * 32;
+        const int64_t r0 = tr * T, k0 = tk * T;
         const float* src = g.src + g.b_tab[b];
-        for (int j = ty; j < 32; j += 8) {
-            // tx runs along the source's fast direction
-            const int64_t r = r0 + (g.src_kfast ? j : tx), k = k0 + (g.src_kfast ? tx : j);
-            float v = 0.f;
-            if (r < g.rows && k < g.K) v = src[g.row_tab[r] + g.k_tab[k]];
-            if (g.src_kfast) tile[j][tx] = v; else tile[tx][j] = v;  // tile[r][k]
+        // tx runs along the source's fast direction: its offset is looked up once per tile, and the
+        // sixteen loads of a thread are all issued before the first one is used
+        const int64_t fast = (g.src_kfast ? k0 : r0) + tx;
+        const bool fast_ok = g.src_kfast ? fast < g.K : fast < g.rows;
+        const int64_t fast_off = fast_ok ? (g.src_kfast ? g.k_tab[fast] : g.row_tab[fast]) : 0;
+        float v[kPer];
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int64_t slow = (g.src_kfast ? r0 : k0) + ty + 4 * i;
+            const bool ok = fast_ok && (g.src_kfast ? slow < g.rows : slow < g.K);
+            v[i] = ok ? src[fast_off + (g.src_kfast ? g.row_tab[slow] : g.k_tab[slow])] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int j = ty + 4 * i;
+            if (g.src_kfast) tile[j][tx] = v[i]; else tile[tx][j] = v[i];  // tile[r][k]
         }
         __syncthreads();
-        for (int j = ty; j < 32; j += 8) {
-            const int64_t r = r0 + j, k = k0 + tx;
-            if (r < g.rows && k < g.Kp) g.dst[(b * g.rows + r) * g.Kp + k] = tile[j][tx];
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int64_t r = r0 + ty + 4 * i, k = k0 + tx;
+            if (r < g.rows && k < g.Kp) g.dst[(b * g.rows + r) * g.Kp + k] = tile[ty + 4 * i][tx];
         }
         __syncthreads();
     }
@@ -1861,7 +1875,18 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
             return (total / o.geom.e1) * o.geom.tiles1 * rows > total + total / 2;
         };
         const int force_pack = env_int("TFB_TC_REPACK", 0);  // bit 0: A, bit 1: B (experiments)
-        const bool pack_a = wasteful(a, M, kBM) || (force_pack & 1), pack_b = wasteful(b, N, half_w ? half_w : rows_b) || (force_pack & 2);
+        bool pack_a = wasteful(a, M, kBM) || (force_pack & 1), pack_b = wasteful(b, N, half_w ? half_w : rows_b) || (force_pack & 2);
+        // An MN-major operand of a large product is also worth one pass: with the corrections as a bf16
+        // MMA the pair kernel converts K-major tiles faster (8192^3 with N(0,1) operands: 296 against
+        // 276 TFLOP/s with A MN-major, 270 with both), the copy runs at 1.9 TB/s, and what it costs is
+        // proportional to the operand while what it saves is proportional to the product: from about
+        // 5000 rows of the OTHER operand on the copy is the cheaper side, and at 8192 it nets 5 %.
+        // Optional: without room for the copy the product runs on the operand as it lies.
+        const bool favour_kmajor = pair && K >= 512 && env_int("TFB_TC_BF16_CORRECTIONS", 1) != 0 && env_int("TFB_TC_REPACK_MN", 1);
+        const bool opt_a = !pack_a && favour_kmajor && a.ok && a.geom.mn_major && N >= 8192;
+        const bool opt_b = !pack_b && favour_kmajor && b.ok && b.geom.mn_major && M >= 8192;
+        pack_a |= opt_a;
+        pack_b |= opt_b;
         if (pack_a || pack_b) {
             TFB_TRY(get_tables(ctx, p, &t));
             ContractArgs ca;
@@ -1869,10 +1894,14 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
             const int64_t Kp = (K + 3) / 4 * 4, Bn = p.B();
             auto repack = [&](int tns, PoolBlock* blk, OperandMap* out) -> tfb_status {
                 const int64_t rows = tns == 0 ? M : N;
-                TFB_TRY(blk->alloc(ctx, (size_t)(rows * Kp * Bn) * sizeof(float)));
+                const tfb_status got = blk->alloc(ctx, (size_t)(rows * Kp * Bn) * sizeof(float));
+                if (got != TFB_OK) {
+                    if (tns == 0 ? opt_a : opt_b) return TFB_OK;  // no room for a copy that only saves time
+                    return got;
+                }
                 RepackArgs r{(const float*)(tns == 0 ? p.a : p.b), tns == 0 ? t->a_m : t->b_n, tns == 0 ? t->a_k : t->b_k,
                              tns == 0 ? t->a_b : t->b_b, rows, K, Kp, Bn, tns == 0 ? ca.a_kfast : ca.b_kfast, (float*)blk->ptr};
-                const int64_t n_tiles = ((rows + 31) / 32) * ((Kp + 31) / 32) * Bn;
+                const int64_t n_tiles = ((rows + kRepackTile - 1) / kRepackTile) * ((Kp + kRepackTile - 1) / kRepackTile) * Bn;
                 {
                     LaunchScope ls(ctx, "repack_operand");
                     repack_kmajor_kernel<<<(unsigned)std::min<int64_t>(n_tiles, (int64_t)ctx->sm_count * 16), 256, 0, ctx->stream>>>(r);

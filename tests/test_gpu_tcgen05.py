@@ -142,6 +142,34 @@ def test_corrections_as_one_bf16_product(tb, oracle, shape, beta, la, lb, spread
     assert not np.array_equal(got, other)  # the switch does select another form of the corrections
 
 
+@pytest.mark.parametrize("shape,la,lb,copies", [((384, 8192, 640), "col", "col", 1), ((8192, 300, 520), "row", "row", 1),
+                                                ((8192, 8192, 512), "col", "row", 2), ((384, 4096, 640), "col", "col", 0),
+                                                ((384, 8192, 640), "row", "col", 0)])
+def test_large_products_copy_mn_major_operands_k_major(tb, oracle, shape, la, lb, copies, monkeypatch):
+    """An operand whose free index is the contiguous one is copied K-major first when the other
+    operand has 8192 rows or more (the copy costs less than the faster conversion of K-major tiles
+    saves); smaller products and K-major operands run as they lie.  Same result either way."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a, b = random_array(rng, (m, k), np.float32), random_array(rng, (k, n), np.float32)
+    ctx = tb.Context.get(0)
+    ctx.profile_begin()
+    got, name = run(tb, a, b, la, lb, tb.ContractKernel.Auto)
+    ctx.synchronize()
+    launched = ctx.profile_read("repack_operand")[0]
+    ctx.profile_end()
+    assert name == "tcgen05_tf32x3"
+    assert launched == copies, (launched, copies)
+    assert oracle.rel_frobenius(got, oracle.np_batched_gemm(a, b)) <= 1e-5
+    monkeypatch.setenv("TFB_TC_REPACK_MN", "0")
+    ctx.profile_begin()
+    other, _ = run(tb, a, b, la, lb, tb.ContractKernel.Auto)
+    ctx.synchronize()
+    assert ctx.profile_read("repack_operand")[0] == 0
+    ctx.profile_end()
+    assert oracle.rel_frobenius(got, other) <= 1e-6
+
+
 @pytest.mark.parametrize("k", [256, 4096])
 def test_bf16_corrections_keep_exact_products_exact(tb, oracle, k):
     """Operands that TF32 holds exactly (small integers) have zero remainders: the correction
