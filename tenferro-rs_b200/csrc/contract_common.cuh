@@ -40,7 +40,6 @@ struct ContractArgs {
     int a_vec, b_vec;      // elements per cp.async (1, or 2 for f64 when 16-byte chunks are legal)
     // Work decomposition: tiles x k-iterations, cut into equal contiguous ranges ("stream-K").
     int64_t tiles_m, tiles_n, n_tiles, k_iters, total_iters, iters_per_cta;
-    int debug;
     unsigned* sk_flags;  // per-CTA flags of the in-kernel stream-K reduction (TMA-fed DMMA kernel)
     unsigned sk_epoch;   // a flag is raised when it equals this launch's epoch
     int sk_two_phase;    // 1: every range parks its sums in its slot; a finishing kernel adds the pieces of a tile

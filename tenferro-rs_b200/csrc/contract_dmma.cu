@@ -194,9 +194,9 @@ __device__ __forceinline__ void dmma_range(const ContractArgs& g, char* smem, in
                 const int64_t nxt = kit + STAGES - 1;
                 int ns = slot + STAGES - 1;
                 if (ns >= STAGES) ns -= STAGES;
-                if (nxt < ke && !(g.debug & 1)) {
+                if (nxt < ke) {
                     issue(ns);
-                    if (!(g.debug & 2)) fetch(nxt + 1);
+                    fetch(nxt + 1);
                 }
                 cp_async_commit();
             }
@@ -500,7 +500,6 @@ tfb_status contract_dmma(tfb_ctx* ctx, const ContractProblem& p, bool* declined,
     TFB_TRY(get_tables(ctx, p, &t));
     ContractArgs a;
     fill_args(p, *t, &a);
-    a.debug = env_int("TFB_DEBUG_SKIP", 0);
     const int shape = env_int("TFB_DMMA_TILE", 0);  // 0 auto, 1 small, 2 big
     const bool use_tma = !env_int("TFB_NO_DMMA_TMA", 0);
     if (p.dtype == TFB_F64) {
