@@ -1883,8 +1883,11 @@ tfb_status contract_tcgen05(tfb_ctx* ctx, const ContractProblem& p, bool* declin
         // 5000 rows of the OTHER operand on the copy is the cheaper side, and at 8192 it nets 5 %.
         // Optional: without room for the copy the product runs on the operand as it lies.
         const bool favour_kmajor = pair && K >= 512 && env_int("TFB_TC_BF16_CORRECTIONS", 1) != 0 && env_int("TFB_TC_REPACK_MN", 1);
-        const bool opt_a = !pack_a && favour_kmajor && a.ok && a.geom.mn_major && N >= 8192;
-        const bool opt_b = !pack_b && favour_kmajor && b.ok && b.geom.mn_major && M >= 8192;
+        // (a copy of at most an eighth of the device's memory: a larger one could take the room that
+        // the caller's next tensors need)
+        const double copy_cap = (double)ctx->total_mem / 8 / sizeof(float);
+        const bool opt_a = !pack_a && favour_kmajor && a.ok && a.geom.mn_major && N >= 8192 && (double)M * K * p.B() <= copy_cap;
+        const bool opt_b = !pack_b && favour_kmajor && b.ok && b.geom.mn_major && M >= 8192 && (double)N * K * p.B() <= copy_cap;
         pack_a |= opt_a;
         pack_b |= opt_b;
         if (pack_a || pack_b) {
